@@ -1,0 +1,136 @@
+/*
+ * sparsebench_b200 -- C ABI of the sync-free block-sparse MoE forward path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and a CUDA stream (no torch types),
+ *   - only enqueues work on that stream: it never synchronises, never reads device memory back
+ *     to the host and never calls cudaMalloc/cudaFree (all buffers belong to the caller),
+ *   - works on the calling thread's current CUDA device,
+ *   - returns SB_OK (0) or a negative-free small positive status code; sb_last_error() gives the
+ *     text for the calling thread's last failure.
+ *
+ * Buffers are sized for the worst case on the host; the real padded row count stays in
+ * padded_offsets[num_experts] on the device and the kernels read it (or the flat tail of
+ * row_offsets) from there. That is what makes the layer capturable in a CUDA graph and replayable
+ * with new tokens and new routing.
+ *
+ * "Reference" below is the SparseBench source tree; each declaration cites the interface it
+ * replaces as path:line inside that tree.
+ */
+#ifndef SPARSEBENCH_B200_H_
+#define SPARSEBENCH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A cudaStream_t. Declared opaquely so that the header needs no CUDA include. */
+typedef struct CUstream_st* sb_stream_t;
+
+enum sb_status {
+  SB_OK = 0,
+  SB_ERR_INVALID_ARGUMENT = 1, /* a size/alignment/range rule of the entry point is violated */
+  SB_ERR_UNSUPPORTED = 2,      /* legal for the reference, not built here (see sb_last_error) */
+  SB_ERR_CUDA = 3,             /* a CUDA runtime/driver call failed (launch, attribute, ...) */
+  SB_ERR_TENSOR_MAP = 4        /* cuTensorMapEncodeTiled rejected a descriptor */
+};
+
+/* Bits of the device-side status word the GEMM kernels write when a bounded wait gives up. */
+enum sb_device_status {
+  SB_DEV_OK = 0,
+  SB_DEV_TIMEOUT_PRODUCER = 1, /* TMA/gather producer waited too long for a free stage */
+  SB_DEV_TIMEOUT_MMA = 2,      /* MMA issuer waited too long for a full stage or a free accumulator */
+  SB_DEV_TIMEOUT_EPILOGUE = 4  /* epilogue waited too long for a finished accumulator */
+};
+
+/* Text of the calling thread's last failure ("" if none). Never NULL. */
+const char* sb_last_error(void);
+/* Short name of a status code. Never NULL. */
+const char* sb_status_string(int code);
+/* Library version, "major.minor.patch". */
+const char* sb_version(void);
+
+/*
+ * Fills out[0..n) with __CUDA_ARCH__ of the device code that actually ran (1000 on B200).
+ * Replaces sparsebench::arch_probe (csrc/smoke.cu:23-38, csrc/ops.hpp:7-11). n must be > 0.
+ */
+int sb_arch_probe(int32_t* out, int64_t n, sb_stream_t stream);
+
+/*
+ * Worst-case sizes of the routing outputs, computed the way the reference host code does
+ * (csrc/routing.cu:213-224): max_row_blocks = (n_copies + num_experts*(block_size-1)) / block_size,
+ * max_rows = max_row_blocks * block_size. Returns SB_ERR_INVALID_ARGUMENT where the reference
+ * raises ("num_experts must be in [1, 1024]", "ffn_dim must be a positive multiple of block_size",
+ * "problem too large for int32 indexing").
+ */
+int sb_route_sizes(int64_t n_copies, int32_t num_experts, int64_t ffn_dim, int64_t block_size,
+                   int64_t* max_row_blocks, int64_t* max_rows, int64_t* ffn_blocks);
+
+/* Bytes of scratch sb_route needs for (n_copies, num_experts). May be 0. */
+size_t sb_route_workspace_bytes(int64_t n_copies, int32_t num_experts);
+
+/*
+ * Routing -> block-sparse layout: a stable counting sort of the n_copies = T*k token copies by
+ * expert (copy c = t*k + j keeps ascending c inside an expert), every expert group padded to a
+ * multiple of block_size, plus the BSR arrays the two matmuls consume. Bit-exact to the
+ * reference's topology.build_topology (sparsebench/topology.py:53-118) and to its CUDA version
+ * build_topology_cuda (csrc/routing.cu:197-281), including the tails of the worst-case buffers:
+ *   row_token[r]       = source token, -1 for padding rows and for rows past the real end
+ *   copy_row[c]        = padded row of copy c, -1 if its expert id was outside [0, num_experts)
+ *   row_block_expert[] = expert of each row block, -1 past the real end
+ *   row_offsets[i]     = min(i, real_row_blocks) * ffn_blocks
+ *   col_indices[]      = expert * ffn_blocks + j, -1 past the real end
+ *   error[0]           = 1 if any expert id was out of range, else 0 (written, not OR-ed)
+ * expert_idx is int32 (idx_is_i64 == 0) or int64. workspace must hold
+ * sb_route_workspace_bytes() bytes (may be NULL when that is 0).
+ */
+int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k, int32_t num_experts,
+             int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
+             int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,
+             int32_t* row_offsets, int32_t* col_indices, int32_t* error, void* workspace,
+             sb_stream_t stream);
+
+/*
+ * SDD: h_blocks[row_offsets[rb] + f/128][r][f%128] = (gelu)(x[row_token[rb*128+r]] . w1[e][:, f])
+ * for every live row block rb (e = row_block_expert[rb]); padding rows (row_token < 0) are
+ * zero-filled inside the load and come out exactly 0. Replaces sparsebench::sdd_cuda
+ * (csrc/sdd.cu:123-170; kernel csrc/sdd.cu:43-114). bf16 in/out, fp32 accumulation on the
+ * tcgen05 tensor cores, exact-erf GELU. Block size is 128; d_model % 64 == 0; ffn_dim % 256 == 0;
+ * x, w1 and h_blocks 16-byte aligned. Row blocks with row_offsets[rb] == row_offsets[rb+1] are
+ * skipped and their blocks left unwritten. dev_status (may be NULL) receives sb_device_status
+ * bits if a bounded device-side wait expires; it is only ever OR-ed into.
+ */
+int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
+           const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
+           int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int32_t* dev_status,
+           sb_stream_t stream);
+
+/*
+ * DSD: y[rb*bs + r][:] = sum over p in [row_offsets[rb], row_offsets[rb+1]) of
+ * h_blocks[p][r][:] . w[col_indices[p]*bs .. +bs][:], a general BSR x dense product.
+ * Replaces sparsebench::dsd_cuda (csrc/dsd.cpp:27-80) and its version-5 kernel
+ * (csrc/dsd_v5.cu:42-123). bf16 in/out, fp32 accumulation. block_size must be 128 and
+ * d_model % 128 == 0 (the reference's block size 64 is not built: SB_ERR_UNSUPPORTED).
+ * Rows of row blocks without blocks are left unwritten, or zeroed when zero_dead_rows != 0
+ * (what the reference's versions 1-3 do).
+ */
+int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
+           const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks, int32_t block_size,
+           int zero_dead_rows, void* y, int32_t* dev_status, sb_stream_t stream);
+
+/*
+ * Combine: out[t][:] = bf16( sum_j float(y[copy_row[t*k+j]][:]) * float(gate[t][j]) ), products and
+ * sums rounded separately in fp32 in the order j = 0..k-1. Replaces the PyTorch lines
+ * sparsebench/moe.py:51-55. gate_dtype: 0 = bf16, 1 = fp32. A copy with copy_row < 0 contributes 0.
+ * d_model % 8 == 0; y and out 16-byte aligned.
+ */
+int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gate_dtype, void* out,
+               int64_t num_tokens, int32_t k, int32_t d_model, sb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSEBENCH_B200_H_ */

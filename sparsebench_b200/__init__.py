@@ -1,0 +1,24 @@
+"""sparsebench_b200: the sync-free block-sparse MoE forward path for NVIDIA B200 (sm_100a).
+
+Drop-in for the reference's hot path: `moe_forward` plus the routing / SDD / DSD operator surface,
+served by hand-written CUDA kernels behind a C ABI (include/sparsebench_b200.h). Importing the
+package does not load the CUDA library; the first operator call does, and fails loudly if it is
+missing. There is no CPU or PyTorch fallback.
+"""
+
+from sparsebench_b200.moe import moe_forward
+from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route_device
+from sparsebench_b200.spmm import combine, dsd, sdd
+from sparsebench_b200.topology import Topology
+
+__all__ = [
+    "DeviceTopology",
+    "Topology",
+    "build_topology_cuda",
+    "combine",
+    "dsd",
+    "moe_forward",
+    "route_device",
+    "sdd",
+]
+__version__ = "0.1.0"

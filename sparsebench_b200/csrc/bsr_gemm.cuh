@@ -1,0 +1,375 @@
+// The tensor-core core shared by the two block-sparse matmuls of the MoE layer (SDD and DSD).
+//
+// One output tile = one 128-row block x kTileN columns, accumulated in fp32 in TMEM by
+// tcgen05.mma (M = 128, N = kTileN, K = 16 per instruction, four per 64-wide K step).
+// The kernel is persistent: grid = number of SMs, every CTA walks tiles blockIdx.x, +gridDim.x, ...
+// over the WORST-CASE tile count and reads from device memory (row_offsets) which row blocks are
+// live, so the host never needs the real row count and dead tiles cost two loads.
+//
+// Warp roles (warp-specialised, nothing but mbarriers between them):
+//   warp 0      lane 0: TMA producer. B tiles (weights, MN-major: [k rows][64 n] boxes, 128-byte
+//               swizzle) for both ops, A tiles (H blocks, K-major) for DSD.
+//   warp 1      lane 0: MMA issuer; the warp also owns the TMEM allocation (2 accumulators).
+//   warps 2-9   epilogue: tcgen05.ld of the finished accumulator (lane quarter = warp % 4, column
+//               half = (warp - 2) / 4), GELU for SDD, bf16 pack, 16-byte global stores. Runs on
+//               accumulator i while the MMA warp fills accumulator i^1.
+//   warps 10-13 SDD only: A gather. Thread r owns padded row r of the row block: 8 cp.async of
+//               16 bytes per K step straight from x[row_token] into the swizzled K-major stage,
+//               zero-filled (no global read) for padding rows; an asynchronous mbarrier arrive
+//               reports completion so the thread can run the full pipeline depth ahead.
+//
+// Shared-memory stage layout (all 1024-byte aligned, as the 128-byte swizzle needs):
+//   A: 128 rows x 128 B; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)      (16 KB)
+//   B: kTileN/64 slabs of [64 k rows x 128 B], same swizzle                          (kTileN*128 B)
+//
+// Every wait is bounded; on expiry the role records a bit in *dev_status, raises the CTA's abort
+// flag and all roles fall through to the common exit, where TMEM is released.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "ptx_sm100.cuh"
+#include "sb_common.cuh"
+
+namespace sb {
+
+enum class GemmOp { kSdd, kDsd };
+
+struct GemmParams {
+  const int32_t* row_offsets;       // [num_row_blocks + 1]
+  int32_t num_row_blocks;           // worst case
+  int32_t num_slices;               // N / kTileN
+  int32_t* dev_status;              // may be null
+  // SDD
+  const __nv_bfloat16* x;           // [T, D]
+  const int32_t* row_token;         // [num_row_blocks * 128]
+  const int32_t* row_block_expert;  // [num_row_blocks]
+  __nv_bfloat16* h_out;             // [nnz, 128, 128]
+  int32_t apply_gelu;
+  // DSD
+  const int32_t* col_indices;       // [nnz]
+  __nv_bfloat16* y;                 // [num_row_blocks * 128, D]
+  int32_t zero_dead_rows;
+  // both
+  int32_t d_model;
+};
+
+template <GemmOp kOp, int kTileN>
+struct GemmConfig {
+  static constexpr int kTileM = 128;
+  static constexpr int kTileK = 64;
+  static constexpr int kUmmaK = 16;
+  static constexpr int kABytes = kTileM * kTileK * 2;          // 16 KB
+  static constexpr int kBSlabBytes = kTileK * 128;             // 64 k rows x 128 B = 8 KB
+  static constexpr int kBSlabs = kTileN / 64;
+  static constexpr int kBBytes = kBSlabs * kBSlabBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = kTileN == 256 ? 4 : 6;
+  static constexpr int kEpilogueWarps = 8;
+  static constexpr int kGatherWarps = kOp == GemmOp::kSdd ? 4 : 0;
+  static constexpr int kFirstEpilogueWarp = 2;
+  static constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
+  static constexpr int kThreads = 32 * (kFirstGatherWarp + kGatherWarps);
+  static constexpr int kTmemColumns = 2 * kTileN;              // two accumulators; 256 or 512
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
+  static constexpr uint32_t kFullArrivals = kOp == GemmOp::kSdd ? 1 + 32 * kGatherWarps : 1;
+  static constexpr uint32_t kTxBytes = kOp == GemmOp::kSdd ? kBBytes : kStageBytes;
+  static_assert(kTileN == 128 || kTileN == 256, "tile width");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+
+template <GemmOp kOp, int kTileN>
+__global__ void __launch_bounds__(GemmConfig<kOp, kTileN>::kThreads, 1)
+bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const GemmParams p) {
+  using Cfg = GemmConfig<kOp, kTileN>;
+  constexpr bool kIsSdd = kOp == GemmOp::kSdd;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_base = smem_base;
+  const uint32_t b_base = smem_base + Cfg::kStages * Cfg::kABytes;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t full_bar = bar_base;                              // [kStages]
+  const uint32_t empty_bar = bar_base + 8 * Cfg::kStages;          // [kStages]
+  const uint32_t acc_full_bar = bar_base + 16 * Cfg::kStages;      // [2]
+  const uint32_t acc_empty_bar = acc_full_bar + 16;                // [2]
+  const uint32_t tmem_slot = acc_empty_bar + 16;                   // uint32
+  const uint32_t abort_slot = tmem_slot + 4;                       // uint32
+  // Generic pointers to the two words the threads read directly.
+  uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
+  volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
+  volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(smem_aligned + (abort_slot - smem_base));
+
+  const int warp = static_cast<int>(threadIdx.x >> 5);
+  const int lane = static_cast<int>(threadIdx.x & 31);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      ptx::mbar_init(full_bar + 8 * s, Cfg::kFullArrivals);
+      ptx::mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(acc_full_bar + 8 * a, 1);
+      ptx::mbar_init(acc_empty_bar + 8 * a, 32 * Cfg::kEpilogueWarps);
+    }
+    *abort_word = 0u;
+    ptx::fence_barrier_init();
+    if (!kIsSdd) ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, Cfg::kTmemColumns);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  ptx::tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_word;
+
+  const int32_t total_tiles = p.num_row_blocks * p.num_slices;
+  auto give_up = [&](int bit) {
+    *abort_word = 1u;
+    if (p.dev_status != nullptr) atomicOr(p.dev_status, bit);
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int32_t rb = tile / p.num_slices;
+        const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
+        const int32_t begin = p.row_offsets[rb];
+        const int32_t end = p.row_offsets[rb + 1];
+        if (begin == end) continue;
+        const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2;
+        const int32_t b_row_base = kIsSdd ? p.row_block_expert[rb] * p.d_model : 0;
+        int32_t col_block = 0;
+        int32_t col_block_next = kIsSdd ? 0 : p.col_indices[begin];
+        for (int32_t ks = 0; ks < k_steps; ++ks) {
+          if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
+            give_up(SB_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full_bar + 8 * stage;
+          ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
+          int32_t b_row;
+          if (kIsSdd) {
+            b_row = b_row_base + ks * Cfg::kTileK;
+          } else {
+            const int32_t blk = begin + (ks >> 1);
+            const int32_t k_half = (ks & 1) * Cfg::kTileK;
+            ptx::tma_load_2d(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * Cfg::kTileM, bar);
+            if ((ks & 1) == 0) {
+              // The next block's column index is fetched one block ahead to keep it off the issue path.
+              col_block = col_block_next;
+              if (blk + 1 < end) col_block_next = p.col_indices[blk + 1];
+            }
+            b_row = col_block * Cfg::kTileM + k_half;
+          }
+          const uint32_t b_dst = b_base + stage * Cfg::kBBytes;
+#pragma unroll
+          for (int j = 0; j < Cfg::kBSlabs; ++j)
+            ptx::tma_load_2d(b_dst + j * Cfg::kBSlabBytes, &map_b, n0 + j * 64, b_row, bar);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t kIdesc = ptx::make_idesc_bf16(Cfg::kTileM, kTileN, /*b_mn_major=*/true);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int32_t rb = tile / p.num_slices;
+        const int32_t begin = p.row_offsets[rb];
+        const int32_t end = p.row_offsets[rb + 1];
+        if (begin == end) continue;
+        const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2;
+        if (!ptx::mbar_wait_bounded(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_word)) {
+          give_up(SB_DEV_TIMEOUT_MMA);
+          break;
+        }
+        ptx::tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        for (int32_t ks = 0; ks < k_steps; ++ks) {
+          if (!ptx::mbar_wait_bounded(full_bar + 8 * stage, phase, abort_word)) {
+            give_up(SB_DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          // The gathered A rows were written through the generic proxy (cp.async); order them
+          // before the tensor core's async-proxy reads.
+          if (kIsSdd) ptx::fence_proxy_async_shared();
+          ptx::tcgen05_fence_after_sync();
+          const uint32_t a_addr = a_base + stage * Cfg::kABytes;
+          const uint32_t b_addr = b_base + stage * Cfg::kBBytes;
+#pragma unroll
+          for (int kk = 0; kk < Cfg::kTileK / Cfg::kUmmaK; ++kk) {
+            // A: 16 K elements = 32 bytes along the swizzled 128-byte row.
+            const uint64_t desc_a = ptx::make_smem_desc(a_addr + kk * 32, 16, 1024);
+            // B: 16 k rows = two 1024-byte groups; slabs of 64 n are kBSlabBytes apart.
+            const uint64_t desc_b = ptx::make_smem_desc(b_addr + kk * 2048, Cfg::kBSlabBytes, 1024);
+            ptx::umma_bf16(d_tmem, desc_a, desc_b, kIdesc, (ks | kk) != 0);
+          }
+          ptx::umma_commit(empty_bar + 8 * stage);  // frees the stage once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(acc_full_bar + 8 * acc);  // accumulator complete
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp < Cfg::kFirstGatherWarp) {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: quarter*32 .. +31
+    const int half = (warp - Cfg::kFirstEpilogueWarp) >> 2;
+    const int row = quarter * 32 + lane;
+    constexpr int kHalfCols = kTileN / 2;
+    uint32_t acc = 0, acc_phase = 0;
+    for (int32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int32_t rb = tile / p.num_slices;
+      const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
+      const int32_t begin = p.row_offsets[rb];
+      const int32_t end = p.row_offsets[rb + 1];
+      if (begin == end) {
+        if (!kIsSdd && p.zero_dead_rows) {
+          uint4* dst = reinterpret_cast<uint4*>(p.y + (static_cast<int64_t>(rb) * Cfg::kTileM + row) * p.d_model + n0 +
+                                                half * kHalfCols);
+#pragma unroll
+          for (int q = 0; q < kHalfCols / 8; ++q) dst[q] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        continue;
+      }
+      if (!ptx::mbar_wait_bounded(acc_full_bar + 8 * acc, acc_phase, abort_word)) {
+        give_up(SB_DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      ptx::tcgen05_fence_after_sync();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN + half * kHalfCols;
+#pragma unroll 1
+      for (int cc = 0; cc < kHalfCols / 32; ++cc) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(t_addr + cc * 32, v);
+        ptx::tmem_ld_wait();
+        const int32_t col = n0 + half * kHalfCols + cc * 32;  // first of 32 output columns
+        __nv_bfloat16* dst;
+        if (kIsSdd) {
+          // FFN column f lives in block begin + f/128, column f%128; 32 columns never straddle a block.
+          dst = p.h_out + ((static_cast<int64_t>(begin) + (col >> 7)) * Cfg::kTileM + row) * 128 + (col & 127);
+        } else {
+          dst = p.y + (static_cast<int64_t>(rb) * Cfg::kTileM + row) * p.d_model + col;
+        }
+        uint4* dst4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            float f0 = __uint_as_float(v[q * 8 + 2 * h]);
+            float f1 = __uint_as_float(v[q * 8 + 2 * h + 1]);
+            if (kIsSdd && p.apply_gelu) {
+              f0 = gelu_erf(f0);
+              f1 = gelu_erf(f1);
+            }
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(f0, f1);
+            packed[h] = *reinterpret_cast<const uint32_t*>(&pair);
+          }
+          dst4[q] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+      ptx::tcgen05_fence_before_sync();
+      ptx::mbar_arrive(acc_empty_bar + 8 * acc);
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  } else if (kIsSdd) {
+    // ---------------------------------------------------------------- A gather (SDD)
+    const int r = (warp - Cfg::kFirstGatherWarp) * 32 + lane;  // padded row inside the row block
+    const uint32_t row_dst = static_cast<uint32_t>(r) * 128u;
+    const uint32_t swz = static_cast<uint32_t>(r & 7);
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int32_t rb = tile / p.num_slices;
+      if (p.row_offsets[rb] == p.row_offsets[rb + 1]) continue;
+      const int32_t token = p.row_token[static_cast<int64_t>(rb) * Cfg::kTileM + r];
+      const bool real = token >= 0;
+      // Padding rows still pass a valid address; the zero-fill form reads nothing from it.
+      const __nv_bfloat16* src = p.x + (real ? static_cast<int64_t>(token) * p.d_model : 0);
+      const int32_t k_steps = p.d_model / Cfg::kTileK;
+      for (int32_t ks = 0; ks < k_steps; ++ks) {
+        if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
+          give_up(SB_DEV_TIMEOUT_PRODUCER);
+          ok = false;
+          break;
+        }
+        const uint32_t dst = a_base + stage * Cfg::kABytes + row_dst;
+        const __nv_bfloat16* s = src + ks * Cfg::kTileK;
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c) ptx::cp_async_16_zfill(dst + ((c ^ swz) << 4), s + c * 8, real);
+        ptx::cp_async_mbar_arrive_noinc(full_bar + 8 * stage);
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    ptx::cp_async_wait_all();
+  }
+
+  // Common exit: every role is done (or has given up); release TMEM.
+  if (*abort_word != 0u) {
+    // Gave up mid-pipeline: leave bulk copies that are still in flight time to land in this CTA's
+    // shared memory before it is handed back.
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  ptx::tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tcgen05_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemColumns);
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+// Encodes a 2-D bf16 row-major tensor map [rows, cols] with a {64 x box_rows} box and 128-byte
+// swizzle. Host only, no synchronisation. Returns SB_OK or records the failure.
+int encode_bf16_2d_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                       const char* what);
+
+// Opt-in to the large dynamic shared memory of one kernel instance, once per device.
+template <GemmOp kOp, int kTileN>
+int prepare_gemm_kernel(int device) {
+  static bool done[kMaxDevices] = {};
+  if (done[device]) return SB_OK;
+  const cudaError_t err =
+      cudaFuncSetAttribute(bsr_gemm_kernel<kOp, kTileN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           GemmConfig<kOp, kTileN>::kSmemBytes);
+  if (err != cudaSuccess) return fail(SB_ERR_CUDA, "shared memory opt-in: %s", cudaGetErrorString(err));
+  done[device] = true;
+  return SB_OK;
+}
+
+template <GemmOp kOp, int kTileN>
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& params, cudaStream_t stream,
+                const char* what) {
+  int device = 0;
+  const DeviceInfo* info = current_device_info(&device);
+  if (info == nullptr) return SB_ERR_CUDA;
+  if (int rc = prepare_gemm_kernel<kOp, kTileN>(device)) return rc;
+  using Cfg = GemmConfig<kOp, kTileN>;
+  const int64_t tiles = static_cast<int64_t>(params.num_row_blocks) * params.num_slices;
+  const unsigned grid = static_cast<unsigned>(tiles < info->sm_count ? tiles : info->sm_count);
+  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, params);
+  return check_launch(what);
+}
+
+}  // namespace sb

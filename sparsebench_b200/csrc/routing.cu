@@ -1,0 +1,449 @@
+// Routing -> block-sparse layout on the device, with no host sync and no atomics.
+//
+// The T*k token copies (copy c = t*k + j) are sorted by expert with a stable counting sort and each
+// expert's group is padded to a multiple of block_size. The result is bit-exact to the reference's
+// topology.build_topology (sparsebench/topology.py:53-118) and build_topology_cuda
+// (csrc/routing.cu:197-281), including the -1 / flat tails of the worst-case sized buffers.
+//
+// How order is kept without atomics: a warp walks a contiguous run of copies 32 at a time, in copy
+// order. Inside one step __match_any_sync gives every lane the set of lanes holding the same
+// expert; the number of those below it is its rank, and the lowest of them alone updates that
+// warp's private per-expert counter. Runs are laid out in copy order (warp 0's run first), so an
+// exclusive scan of the counters over (chunk, warp) for each expert gives every run its base, and
+// base + running count + rank is the copy's position inside its expert. Nothing depends on which
+// thread wins a race, so two launches always agree.
+//
+// Two launch shapes:
+//   small (n <= kSingleCtaMaxCopies): ONE block of 1024 threads does count, scan, scatter and the
+//       layout arrays. This is the hot-path shape (8192 copies per layer call).
+//   large: chunk histograms -> one-block scan -> scatter + layout, three launches.
+// Padding rows and rows past the real end get row_token = -1 from the layout pass itself (a row
+// is written exactly once, by the scatter or by the fill), so no memset is needed.
+
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kMaxExperts = 1024;  // one thread per expert in the scan block (reference: csrc/routing.cu:31)
+constexpr unsigned kFullMask = 0xffffffffu;
+constexpr int64_t kSingleCtaMaxCopies = 32768;
+constexpr int kSingleCtaThreads = 1024;
+constexpr int kChunkThreads = 256;
+constexpr int kChunkWarps = kChunkThreads / 32;
+constexpr int kChunkCopies = 2048;  // copies per block in the large shape
+constexpr int kLayoutThreads = 256;
+
+template <typename index_t>
+__device__ __forceinline__ int32_t read_expert(const index_t* __restrict__ expert_idx, int64_t c, int64_t end,
+                                               int32_t num_experts, bool& bad) {
+  if (c >= end) return -1;
+  const index_t v = expert_idx[c];
+  if (v >= 0 && v < static_cast<index_t>(num_experts)) return static_cast<int32_t>(v);
+  bad = true;  // skipped: nothing is written for it except copy_row = -1
+  return -1;
+}
+
+// One warp adds its run [begin, end) to its private counters. Returns true if it saw a bad id.
+template <typename index_t>
+__device__ bool warp_count_run(const index_t* __restrict__ expert_idx, int64_t begin, int64_t end,
+                               int32_t num_experts, int32_t* counters, int lane) {
+  bool bad = false;
+  for (int64_t c0 = begin; c0 < end; c0 += 32) {
+    const int32_t e = read_expert(expert_idx, c0 + lane, end, num_experts, bad);
+    const bool valid = e >= 0;
+    const unsigned active = __ballot_sync(kFullMask, valid);
+    if (valid) {
+      const unsigned peers = __match_any_sync(active, e);
+      if ((peers & ((1u << lane) - 1u)) == 0) counters[e] += __popc(peers);  // one writer per expert
+    }
+    __syncwarp();
+  }
+  return bad;
+}
+
+// One warp places its run. counters[e] holds the number of copies of e that come before this run
+// (all earlier chunks and warps) and is advanced as the run is walked.
+template <typename index_t>
+__device__ void warp_scatter_run(const index_t* __restrict__ expert_idx, int64_t begin, int64_t end,
+                                 int32_t num_experts, int32_t k, int32_t* counters,
+                                 const int32_t* padded_offsets, int32_t* __restrict__ copy_row,
+                                 int32_t* __restrict__ row_token, int lane) {
+  bool bad = false;
+  for (int64_t c0 = begin; c0 < end; c0 += 32) {
+    const int64_t c = c0 + lane;
+    const int32_t e = read_expert(expert_idx, c, end, num_experts, bad);
+    const bool valid = e >= 0;
+    const unsigned active = __ballot_sync(kFullMask, valid);
+    unsigned peers = 0, lower = 0;
+    int32_t before = 0;
+    if (valid) {
+      peers = __match_any_sync(active, e);
+      lower = peers & ((1u << lane) - 1u);
+      before = counters[e];
+    }
+    __syncwarp();
+    if (valid && lower == 0) counters[e] = before + __popc(peers);
+    __syncwarp();
+    if (valid) {
+      const int32_t row = padded_offsets[e] + before + __popc(lower);
+      copy_row[c] = row;
+      row_token[row] = static_cast<int32_t>(c / k);
+    } else if (c < end) {
+      copy_row[c] = -1;
+    }
+  }
+}
+
+// Exclusive scan of one value per thread over the whole block (blockDim.x <= 1024, multiple of 32).
+__device__ int32_t block_exclusive_scan(int32_t value, int32_t* warp_sums /* [32] shared */, int32_t* total) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  int32_t inclusive = value;
+  for (int d = 1; d < 32; d <<= 1) {
+    const int32_t below = __shfl_up_sync(kFullMask, inclusive, d);
+    if (lane >= d) inclusive += below;
+  }
+  if (lane == 31) warp_sums[warp] = inclusive;
+  __syncthreads();
+  if (warp == 0) {
+    const int num_warps = blockDim.x >> 5;
+    int32_t s = lane < num_warps ? warp_sums[lane] : 0;
+    for (int d = 1; d < 32; d <<= 1) {
+      const int32_t below = __shfl_up_sync(kFullMask, s, d);
+      if (lane >= d) s += below;
+    }
+    warp_sums[lane] = s;  // inclusive over warps
+  }
+  __syncthreads();
+  const int32_t base = warp > 0 ? warp_sums[warp - 1] : 0;
+  if (total != nullptr) *total = warp_sums[(blockDim.x >> 5) - 1];
+  return base + inclusive - value;
+}
+
+struct LayoutOut {
+  int32_t* row_token;
+  int32_t* row_block_expert;
+  int32_t* row_offsets;
+  int32_t* col_indices;
+};
+
+// Fills every worst-case slot the scatter does not write. `warp_index` of `warp_count` warps share
+// the row blocks. offsets[E+1] and counts[E] may be in shared or global memory.
+__device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32_t num_experts, int32_t block_size,
+                            int32_t ffn_blocks, int32_t max_row_blocks, const LayoutOut& out, int warp_index,
+                            int warp_count, int lane) {
+  const int32_t num_row_blocks = offsets[num_experts] / block_size;
+  for (int32_t rb = warp_index; rb < max_row_blocks; rb += warp_count) {
+    int32_t expert = -1;
+    int32_t real_rows = 0;
+    if (rb < num_row_blocks) {
+      // Last expert whose range starts at or before this row block: skips empty experts, which
+      // share a start with their successor (reference: csrc/routing.cu:181-189).
+      const int32_t row0 = rb * block_size;
+      int32_t lo = 0, hi = num_experts - 1;
+      while (lo < hi) {
+        const int32_t mid = (lo + hi + 1) >> 1;
+        if (offsets[mid] <= row0) lo = mid; else hi = mid - 1;
+      }
+      expert = lo;
+      real_rows = counts[expert] - (row0 - offsets[expert]);
+      real_rows = max(0, min(block_size, real_rows));
+    }
+    const int64_t row_base = static_cast<int64_t>(rb) * block_size;
+    for (int32_t j = real_rows + lane; j < block_size; j += 32) out.row_token[row_base + j] = -1;
+    const int64_t col_base = static_cast<int64_t>(rb) * ffn_blocks;
+    for (int32_t j = lane; j < ffn_blocks; j += 32)
+      out.col_indices[col_base + j] = expert < 0 ? -1 : expert * ffn_blocks + j;
+    if (lane == 0) {
+      out.row_block_expert[rb] = expert;
+      out.row_offsets[rb] = min(rb, num_row_blocks) * ffn_blocks;
+    }
+  }
+  if (warp_index == 0 && lane == 0) out.row_offsets[max_row_blocks] = min(max_row_blocks, num_row_blocks) * ffn_blocks;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Small shape: everything in one block.
+// Shared memory: counters[32][E] | offsets[E+1] | counts[E] | warp_sums[32].
+template <typename index_t>
+__global__ void __launch_bounds__(kSingleCtaThreads, 1)
+route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t k, int32_t num_experts,
+                          int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
+                          int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
+                          int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
+  extern __shared__ int32_t smem[];
+  constexpr int kWarps = kSingleCtaThreads / 32;
+  int32_t* counters = smem;                                // [kWarps][E]
+  int32_t* offsets = counters + kWarps * num_experts;      // [E + 1]
+  int32_t* counts = offsets + num_experts + 1;             // [E]
+  int32_t* warp_sums = counts + num_experts;               // [32]
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kWarps * num_experts; i += kSingleCtaThreads) counters[i] = 0;
+  __syncthreads();
+
+  // Runs of equal length, a multiple of 32, in copy order.
+  const int64_t run = static_cast<int64_t>((n + kSingleCtaThreads - 1) / kSingleCtaThreads) * 32;
+  const int64_t begin = min(static_cast<int64_t>(n), warp * run);
+  const int64_t end = min(static_cast<int64_t>(n), begin + run);
+  const bool bad = warp_count_run(expert_idx, begin, end, num_experts, counters + warp * num_experts, lane);
+  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  if (threadIdx.x == 0) error[0] = any_bad ? 1 : 0;
+
+  // Per expert: exclusive scan over the warps (in place), total = copies of that expert.
+  int32_t total = 0;
+  const int e = threadIdx.x;
+  if (e < num_experts) {
+    for (int w = 0; w < kWarps; ++w) {
+      int32_t* slot = counters + w * num_experts + e;
+      const int32_t c = *slot;
+      *slot = total;
+      total += c;
+    }
+    counts[e] = total;
+    tokens_per_expert[e] = total;
+  }
+  const int32_t padded = e < num_experts ? (total + block_size - 1) / block_size * block_size : 0;
+  int32_t all_rows = 0;
+  const int32_t start = block_exclusive_scan(padded, warp_sums, &all_rows);
+  if (e < num_experts) {
+    offsets[e] = start;
+    padded_offsets[e] = start;
+  }
+  if (e == 0) {
+    offsets[num_experts] = all_rows;
+    padded_offsets[num_experts] = all_rows;
+  }
+  __syncthreads();
+
+  warp_scatter_run(expert_idx, begin, end, num_experts, k, counters + warp * num_experts, offsets, copy_row,
+                   layout.row_token, lane);
+  fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, warp, kWarps, lane);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Large shape, launch 1: per-chunk histograms. chunk_counts[chunk][e], chunk_error[chunk].
+template <typename index_t>
+__global__ void __launch_bounds__(kChunkThreads)
+route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int32_t num_experts,
+                         int32_t* __restrict__ chunk_counts, int32_t* __restrict__ chunk_error) {
+  extern __shared__ int32_t smem[];  // counters[kChunkWarps][E]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
+  __syncthreads();
+
+  constexpr int64_t kRun = kChunkCopies / kChunkWarps;
+  const int64_t begin = min(n, static_cast<int64_t>(blockIdx.x) * kChunkCopies + warp * kRun);
+  const int64_t end = min(n, begin + kRun);
+  const bool bad = warp_count_run(expert_idx, begin, end, num_experts, smem + warp * num_experts, lane);
+  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  if (threadIdx.x == 0) chunk_error[blockIdx.x] = any_bad;
+
+  int32_t* out = chunk_counts + static_cast<int64_t>(blockIdx.x) * num_experts;
+  for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
+    int32_t total = 0;
+#pragma unroll
+    for (int w = 0; w < kChunkWarps; ++w) total += smem[w * num_experts + e];
+    out[e] = total;
+  }
+}
+
+// Large shape, launch 2: one block, one thread per expert. chunk_counts becomes, in place, the
+// number of copies of each expert in all earlier chunks.
+__global__ void __launch_bounds__(kMaxExperts, 1)
+route_scan_kernel(int32_t* __restrict__ chunk_counts, const int32_t* __restrict__ chunk_error, int32_t num_chunks,
+                  int32_t num_experts, int32_t block_size, int32_t* __restrict__ tokens_per_expert,
+                  int32_t* __restrict__ padded_offsets, int32_t* __restrict__ error) {
+  __shared__ int32_t warp_sums[32];
+  const int e = threadIdx.x;
+  int32_t total = 0;
+  if (e < num_experts) {
+    for (int32_t b = 0; b < num_chunks; ++b) {
+      int32_t* slot = chunk_counts + static_cast<int64_t>(b) * num_experts + e;
+      const int32_t c = *slot;
+      *slot = total;
+      total += c;
+    }
+    tokens_per_expert[e] = total;
+  }
+  int bad = 0;
+  for (int32_t b = threadIdx.x; b < num_chunks; b += blockDim.x) bad |= chunk_error[b];
+  const int any_bad = __syncthreads_or(bad);
+  if (threadIdx.x == 0) error[0] = any_bad ? 1 : 0;
+
+  const int32_t padded = e < num_experts ? (total + block_size - 1) / block_size * block_size : 0;
+  int32_t all_rows = 0;
+  const int32_t start = block_exclusive_scan(padded, warp_sums, &all_rows);
+  if (e < num_experts) padded_offsets[e] = start;
+  if (e == 0) padded_offsets[num_experts] = all_rows;
+}
+
+// Large shape, launch 3: blocks [0, num_chunks) place their chunk; the remaining blocks fill the
+// layout arrays and the -1 rows.
+template <typename index_t>
+__global__ void __launch_bounds__(kChunkThreads)
+route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, int32_t k, int32_t num_experts,
+                            int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t num_chunks,
+                            const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ tokens_per_expert,
+                            const int32_t* __restrict__ padded_offsets, int32_t* __restrict__ copy_row,
+                            LayoutOut layout) {
+  extern __shared__ int32_t smem[];  // counters[kChunkWarps][E]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+
+  if (static_cast<int32_t>(blockIdx.x) >= num_chunks) {
+    const int part = static_cast<int>(blockIdx.x) - num_chunks;
+    const int parts = static_cast<int>(gridDim.x) - num_chunks;
+    fill_layout(padded_offsets, tokens_per_expert, num_experts, block_size, ffn_blocks, max_row_blocks, layout,
+                part * kChunkWarps + warp, parts * kChunkWarps, lane);
+    return;
+  }
+
+  for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
+  __syncthreads();
+  constexpr int64_t kRun = kChunkCopies / kChunkWarps;
+  const int64_t begin = min(n, static_cast<int64_t>(blockIdx.x) * kChunkCopies + warp * kRun);
+  const int64_t end = min(n, begin + kRun);
+  warp_count_run(expert_idx, begin, end, num_experts, smem + warp * num_experts, lane);
+  __syncthreads();
+  const int32_t* base = chunk_base + static_cast<int64_t>(blockIdx.x) * num_experts;
+  for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
+    int32_t running = base[e];
+#pragma unroll
+    for (int w = 0; w < kChunkWarps; ++w) {
+      int32_t* slot = smem + w * num_experts + e;
+      const int32_t c = *slot;
+      *slot = running;
+      running += c;
+    }
+  }
+  __syncthreads();
+  warp_scatter_run(expert_idx, begin, end, num_experts, k, smem + warp * num_experts, padded_offsets, copy_row,
+                   layout.row_token, lane);
+}
+
+size_t single_block_smem_bytes(int32_t num_experts) {
+  return (static_cast<size_t>(kSingleCtaThreads / 32) * num_experts + 2 * static_cast<size_t>(num_experts) + 1 + 32) *
+         sizeof(int32_t);
+}
+
+int64_t num_chunks_for(int64_t n) { return (n + kChunkCopies - 1) / kChunkCopies; }
+
+template <typename index_t>
+int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_experts, int32_t ffn_blocks,
+                 int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert, int32_t* padded_offsets,
+                 int32_t* copy_row, const LayoutOut& layout, int32_t* error, void* workspace, cudaStream_t stream) {
+  int device = 0;
+  const DeviceInfo* info = current_device_info(&device);
+  if (info == nullptr) return SB_ERR_CUDA;
+
+  if (n <= kSingleCtaMaxCopies) {
+    static bool attr_done[kMaxDevices] = {};
+    const size_t smem = single_block_smem_bytes(num_experts);
+    if (!attr_done[device]) {
+      const cudaError_t err = cudaFuncSetAttribute(route_single_block_kernel<index_t>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(single_block_smem_bytes(kMaxExperts)));
+      if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
+      attr_done[device] = true;
+    }
+    route_single_block_kernel<index_t><<<1, kSingleCtaThreads, smem, stream>>>(
+        expert_idx, static_cast<int32_t>(n), k, num_experts, ffn_blocks, block_size, max_row_blocks,
+        tokens_per_expert, padded_offsets, copy_row, layout, error);
+    return check_launch("routing (single block)");
+  }
+
+  const int64_t num_chunks = num_chunks_for(n);
+  int32_t* chunk_counts = static_cast<int32_t*>(workspace);
+  int32_t* chunk_error = chunk_counts + num_chunks * num_experts;
+  const size_t smem = static_cast<size_t>(kChunkWarps) * num_experts * sizeof(int32_t);  // <= 32 KB
+
+  route_chunk_count_kernel<index_t><<<static_cast<unsigned>(num_chunks), kChunkThreads, smem, stream>>>(
+      expert_idx, n, num_experts, chunk_counts, chunk_error);
+  if (int rc = check_launch("routing (chunk count)")) return rc;
+
+  route_scan_kernel<<<1, kMaxExperts, 0, stream>>>(chunk_counts, chunk_error, static_cast<int32_t>(num_chunks),
+                                                   num_experts, block_size, tokens_per_expert, padded_offsets,
+                                                   error);
+  if (int rc = check_launch("routing (scan)")) return rc;
+
+  // Enough layout blocks to cover the row blocks a few per warp, at most a few waves.
+  int64_t layout_blocks = (static_cast<int64_t>(max_row_blocks) + kChunkWarps * 4 - 1) / (kChunkWarps * 4);
+  const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
+  if (layout_blocks > cap) layout_blocks = cap;
+  if (layout_blocks < 1) layout_blocks = 1;
+  route_scatter_layout_kernel<index_t>
+      <<<static_cast<unsigned>(num_chunks + layout_blocks), kChunkThreads, smem, stream>>>(
+          expert_idx, n, k, num_experts, ffn_blocks, block_size, max_row_blocks, static_cast<int32_t>(num_chunks),
+          chunk_counts, tokens_per_expert, padded_offsets, copy_row, layout);
+  return check_launch("routing (scatter + layout)");
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" {
+
+int sb_route_sizes(int64_t n_copies, int32_t num_experts, int64_t ffn_dim, int64_t block_size,
+                   int64_t* max_row_blocks, int64_t* max_rows, int64_t* ffn_blocks) {
+  sb::clear_error();
+  constexpr int64_t kI32Max = INT32_MAX;
+  if (n_copies <= 0) return sb::fail(SB_ERR_INVALID_ARGUMENT, "expert_idx must be [T, k] with T, k > 0");
+  if (num_experts <= 0 || num_experts > sb::kMaxExperts)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "num_experts must be in [1, %d], got %d", sb::kMaxExperts, num_experts);
+  if (block_size <= 0 || block_size > kI32Max)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "block_size must be in [1, 2^31)");
+  if (ffn_dim <= 0 || ffn_dim % block_size != 0)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ffn_dim (%lld) must be a positive multiple of block_size (%lld)",
+                    (long long)ffn_dim, (long long)block_size);
+  // Worst case: every expert wastes block_size - 1 rows of padding (reference: csrc/routing.cu:213-216).
+  const int64_t rb = (n_copies + static_cast<int64_t>(num_experts) * (block_size - 1)) / block_size;
+  const int64_t rows = rb * block_size;
+  const int64_t fb = ffn_dim / block_size;
+  if (n_copies > kI32Max || rows > kI32Max / ffn_dim || rb * fb >= kI32Max)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "problem too large for int32 indexing");
+  if (max_row_blocks != nullptr) *max_row_blocks = rb;
+  if (max_rows != nullptr) *max_rows = rows;
+  if (ffn_blocks != nullptr) *ffn_blocks = fb;
+  return SB_OK;
+}
+
+size_t sb_route_workspace_bytes(int64_t n_copies, int32_t num_experts) {
+  if (n_copies <= sb::kSingleCtaMaxCopies || num_experts <= 0) return 0;
+  const int64_t chunks = sb::num_chunks_for(n_copies);
+  return static_cast<size_t>(chunks) * (static_cast<size_t>(num_experts) + 1) * sizeof(int32_t);
+}
+
+int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k, int32_t num_experts,
+             int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
+             int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,
+             int32_t* row_offsets, int32_t* col_indices, int32_t* error, void* workspace, sb_stream_t stream) {
+  sb::clear_error();
+  if (k <= 0 || ffn_blocks <= 0) return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: k and ffn_blocks must be positive");
+  int64_t want_rb = 0;
+  if (int rc = sb_route_sizes(n_copies, num_experts, static_cast<int64_t>(ffn_blocks) * block_size, block_size,
+                              &want_rb, nullptr, nullptr))
+    return rc;
+  if (want_rb != max_row_blocks)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: max_row_blocks is %d, worst case needs %lld", max_row_blocks,
+                    (long long)want_rb);
+  if (!expert_idx || !tokens_per_expert || !padded_offsets || !row_token || !copy_row || !row_block_expert ||
+      !row_offsets || !col_indices || !error)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: NULL buffer");
+  if (workspace == nullptr && sb_route_workspace_bytes(n_copies, num_experts) != 0)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: workspace is NULL but %zu bytes are needed",
+                    sb_route_workspace_bytes(n_copies, num_experts));
+
+  const sb::LayoutOut layout{row_token, row_block_expert, row_offsets, col_indices};
+  const cudaStream_t s = sb::as_stream(stream);
+  if (idx_is_i64)
+    return sb::launch_route(static_cast<const int64_t*>(expert_idx), n_copies, k, num_experts, ffn_blocks, block_size,
+                            max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
+  return sb::launch_route(static_cast<const int32_t*>(expert_idx), n_copies, k, num_experts, ffn_blocks, block_size,
+                          max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
+}
+
+}  // extern "C"

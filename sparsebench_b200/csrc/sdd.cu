@@ -1,0 +1,48 @@
+// SDD entry point: the first MoE matmul, H = (gelu)(gather(x) @ W1[expert]), written straight into
+// the block-sparse (BSR) block list. Argument rules follow the reference host function
+// sparsebench::sdd_cuda (csrc/sdd.cu:123-170); the kernel is bsr_gemm_kernel<kSdd, 256>.
+
+#include "bsr_gemm.cuh"
+
+extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
+                      const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model,
+                      int32_t ffn_dim, int32_t num_experts, int32_t num_row_blocks, int apply_gelu,
+                      int32_t* dev_status, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!x || !w1 || !row_token || !row_block_expert || !row_offsets)
+    return fail(SB_ERR_INVALID_ARGUMENT, "sdd: NULL buffer");
+  if (num_tokens <= 0 || num_experts <= 0 || num_row_blocks < 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "sdd: x must be [T, D] and w1 [E, D, F] with T, E > 0");
+  if (d_model <= 0 || d_model % 64 != 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "sdd needs D (%d) to be a multiple of 64", d_model);
+  if (ffn_dim <= 0 || ffn_dim % 256 != 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "sdd needs F (%d) to be a multiple of 256", ffn_dim);
+  if (!aligned16(x) || !aligned16(w1) || !aligned16(h_blocks))
+    return fail(SB_ERR_INVALID_ARGUMENT, "x, w1 and the output blocks must be 16-byte aligned");
+  const int64_t w_rows = static_cast<int64_t>(num_experts) * d_model;
+  if (w_rows > INT32_MAX || static_cast<int64_t>(ffn_dim) * d_model > INT32_MAX ||
+      static_cast<int64_t>(num_row_blocks) * (ffn_dim / 256) > INT32_MAX)
+    return fail(SB_ERR_INVALID_ARGUMENT, "sdd: problem too large");
+  if (num_row_blocks == 0) return SB_OK;
+  if (!h_blocks) return fail(SB_ERR_INVALID_ARGUMENT, "sdd: NULL output");
+
+  CUtensorMap map_a{};  // unused by SDD: its A rows are gathered by cp.async
+  CUtensorMap map_b;
+  if (int rc = encode_bf16_2d_map(&map_b, w1, static_cast<uint64_t>(w_rows), static_cast<uint64_t>(ffn_dim), 64,
+                                  "sdd (w1)"))
+    return rc;
+
+  GemmParams params{};
+  params.row_offsets = row_offsets;
+  params.num_row_blocks = num_row_blocks;
+  params.num_slices = ffn_dim / 256;
+  params.dev_status = dev_status;
+  params.x = static_cast<const __nv_bfloat16*>(x);
+  params.row_token = row_token;
+  params.row_block_expert = row_block_expert;
+  params.h_out = static_cast<__nv_bfloat16*>(h_blocks);
+  params.apply_gelu = apply_gelu ? 1 : 0;
+  params.d_model = d_model;
+  return launch_gemm<GemmOp::kSdd, 256>(map_a, map_b, params, as_stream(stream), "sdd");
+}
