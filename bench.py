@@ -312,6 +312,19 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     print(json.dumps(line))
 
 
+def run_profile(args: argparse.Namespace) -> None:
+    """Three eager layer calls and nothing else: the command to put under ncu."""
+    from sparsebench_b200 import moe_forward
+
+    cfg = CONFIGS[args.workload or "fine_grained"]
+    torch.cuda.set_device(0)
+    dev = make_layer(cfg, seed=0).to("cuda:0")
+    for _ in range(3):
+        moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile": cfg.name, "layer_calls": 3}))
+
+
 def run_expert_parallel(args: argparse.Namespace) -> None:
     from sparsebench_b200 import ep_bench
 
@@ -326,9 +339,12 @@ def main() -> None:
     parser.add_argument("--workload", default=None, choices=sorted(CONFIGS))
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.profile:
+        run_profile(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     elif args.gpus == 1 and "RANK" not in os.environ:
         run_single_gpu(args)
