@@ -94,6 +94,34 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
              sb_stream_t stream);
 
 /*
+ * Routing for callers that cannot allocate device memory. No counterpart in the reference, whose
+ * host code takes its scratch from PyTorch's allocator (csrc/routing.cu:238); this library's own
+ * sb_route leaves the scratch to the caller instead. Some callers have no allocator to ask: a
+ * language binding that only passes pointers through, a serving process that forbids cudaMalloc
+ * after start-up (it synchronises the whole device, which is exactly what this path exists to
+ * avoid), or code that runs where allocating would break the surrounding framework's rules.
+ * For them this entry point does what sb_route does, with the same inputs, outputs and results,
+ * and keeps the chunk histograms of the large launch shape in an array built into the library:
+ * SB_ROUTE_STATIC_SCRATCH_BYTES of device memory that every GPU which loads the library holds
+ * until the process exits. It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Sizes whose scratch (sb_route_workspace_bytes) exceeds the array are rejected with
+ *     SB_ERR_INVALID_ARGUMENT and a message that names both numbers; 1 MiB covers e.g. 200 000
+ *     copies over 1024 experts, or 8 million copies over 64 experts. Up to 32768 copies no
+ *     scratch is touched at all.
+ *   - The first call on a device looks the array's device address up (once per device, with that
+ *     device current). Make that first call outside of any stream capture.
+ *   - All calls share the one array, which simply keeps whatever the last call left in it; nothing
+ *     in it needs to start at zero. Two calls whose kernels can overlap on the GPU (different
+ *     streams, no dependency) would race on it: order them.
+ */
+#define SB_ROUTE_STATIC_SCRATCH_BYTES (1u << 20)
+int sb_route_static_scratch(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k,
+                            int32_t num_experts, int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
+                            int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* row_token,
+                            int32_t* copy_row, int32_t* row_block_expert, int32_t* row_offsets,
+                            int32_t* col_indices, int32_t* error, sb_stream_t stream);
+
+/*
  * SDD: h_blocks[row_offsets[rb] + f/128][r][f%128] = (gelu)(x[row_token[rb*128+r]] . w1[e][:, f])
  * for every live row block rb (e = row_block_expert[rb]); padding rows (row_token < 0) are
  * zero-filled inside the load and come out exactly 0. Replaces sparsebench::sdd_cuda

@@ -25,6 +25,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "sb_route_workspace_bytes": (c_size_t, [c_int64, c_int32]),
     "sb_route": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
                          _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "sb_route_static_scratch": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                        _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, _P, _P]),
     "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P]),
     "sb_combine": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int32, c_int32, _P]),

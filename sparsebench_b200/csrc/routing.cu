@@ -382,6 +382,31 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   return check_launch("routing (scatter + layout)");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for sb_route_static_scratch: the chunk histograms of the three-launch shape live
+// in this array instead of a caller-provided workspace. Every GPU that loads the library carries
+// these SB_ROUTE_STATIC_SCRATCH_BYTES until the process exits. In host code the array's name is only
+// a stand-in for the symbol; the device address is asked for once per device below.
+constexpr size_t kStaticScratchBytes = SB_ROUTE_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) int32_t g_route_static_scratch[kStaticScratchBytes / sizeof(int32_t)];
+
+// Device address of the array on the calling thread's current device. The first call on a device
+// asks the runtime for it (cudaGetSymbolAddress, with that device current); later calls read a table.
+int static_scratch_address(void** out) {
+  static void* address[kMaxDevices] = {};
+  int device = 0;
+  if (current_device_info(&device) == nullptr) return SB_ERR_CUDA;
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_route_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr)
+      return fail(SB_ERR_CUDA, "routing (static scratch): cudaGetSymbolAddress: %s", cudaGetErrorString(err));
+    address[device] = ptr;
+  }
+  *out = address[device];
+  return SB_OK;
+}
+
 }  // namespace
 }  // namespace sb
 
@@ -444,6 +469,27 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
                             max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
   return sb::launch_route(static_cast<const int32_t*>(expert_idx), n_copies, k, num_experts, ffn_blocks, block_size,
                           max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
+}
+
+int sb_route_static_scratch(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k,
+                            int32_t num_experts, int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
+                            int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* row_token,
+                            int32_t* copy_row, int32_t* row_block_expert, int32_t* row_offsets,
+                            int32_t* col_indices, int32_t* error, sb_stream_t stream) {
+  sb::clear_error();
+  const size_t needed = sb_route_workspace_bytes(n_copies, num_experts);
+  if (needed > sb::kStaticScratchBytes)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT,
+                    "routing (static scratch): %lld copies over %d experts need %zu bytes of scratch, the built-in "
+                    "array holds %zu; use sb_route with a workspace of your own",
+                    (long long)n_copies, num_experts, needed, sb::kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (int rc = sb::static_scratch_address(&scratch)) return rc;
+  // Nothing in the array has to start at zero: every chunk writes all of its counters and its
+  // error word before the scan reads them, so the previous call's contents are simply overwritten.
+  return sb_route(expert_idx, idx_is_i64, n_copies, k, num_experts, ffn_blocks, block_size, max_row_blocks,
+                  tokens_per_expert, padded_offsets, row_token, copy_row, row_block_expert, row_offsets,
+                  col_indices, error, scratch, stream);
 }
 
 }  // extern "C"
