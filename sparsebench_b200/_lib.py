@@ -8,6 +8,7 @@ the prebuilt file next to this module is used.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
@@ -40,7 +41,9 @@ class SparseBenchError(RuntimeError):
 
 
 def library_path() -> Path:
-    return _build.LIB_PATH
+    """The in-tree build, or the file SPARSEBENCH_B200_LIB names (to try another build of the same ABI)."""
+    override = os.environ.get("SPARSEBENCH_B200_LIB")
+    return Path(override) if override else _build.LIB_PATH
 
 
 def load() -> ctypes.CDLL:

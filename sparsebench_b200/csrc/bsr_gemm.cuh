@@ -13,10 +13,11 @@
 //   warps 2-9   epilogue: tcgen05.ld of the finished accumulator (lane quarter = warp % 4, column
 //               half = (warp - 2) / 4), GELU for SDD, bf16 pack, 16-byte global stores. Runs on
 //               accumulator i while the MMA warp fills accumulator i^1.
-//   warps 10-13 SDD only: A gather. Thread r owns padded row r of the row block: 8 cp.async of
-//               16 bytes per K step straight from x[row_token] into the swizzled K-major stage,
-//               zero-filled (no global read) for padding rows; an asynchronous mbarrier arrive
-//               reports completion so the thread can run the full pipeline depth ahead.
+//   warps 10-13 SDD only: A gather. Per K step each thread issues 8 cp.async of 16 bytes straight
+//               from x[row_token] into the swizzled K-major stage; eight lanes share a row, so a warp
+//               instruction moves four whole 128-byte row segments. Padding rows use the zero-fill
+//               form (no global read). An asynchronous mbarrier arrive reports completion, so the
+//               threads run the full pipeline depth ahead without ever waiting for their data.
 //
 // Shared-memory stage layout (all 1024-byte aligned, as the 128-byte swizzle needs):
 //   A: 128 rows x 128 B; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)      (16 KB)
@@ -293,32 +294,54 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else if (kIsSdd) {
     // ---------------------------------------------------------------- A gather (SDD)
-    const int r = (warp - Cfg::kFirstGatherWarp) * 32 + lane;  // padded row inside the row block
-    const uint32_t row_dst = static_cast<uint32_t>(r) * 128u;
-    const uint32_t swz = static_cast<uint32_t>(r & 7);
+    // Lane l = (g, c): g = l >> 3 picks one of four rows, c = l & 7 the 16-byte chunk of the 128-byte
+    // K step, so one warp instruction moves four whole 128-byte row segments (coalesced in global
+    // memory, conflict-free in shared memory). Warp gw covers rows j*16 + gw*4 + g, j = 0..7.
+    const int gw = warp - Cfg::kFirstGatherWarp;
+    const int row0 = gw * 4 + (lane >> 3);  // row for j = 0; rows for other j differ by multiples of 16
+    const uint32_t chunk = static_cast<uint32_t>(lane & 7);
+    const uint32_t dst_off = static_cast<uint32_t>(row0) * 128u + ((chunk ^ static_cast<uint32_t>(row0 & 7)) << 4);
+    auto load_tokens = [&](int32_t tile, int32_t (&tok)[8]) {
+      const int32_t* rows = p.row_token + static_cast<int64_t>(tile / p.num_slices) * Cfg::kTileM + row0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tok[j] = __ldg(rows + j * 16);
+    };
     uint32_t stage = 0, phase = 0;
     bool ok = true;
-    for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    int32_t tile = blockIdx.x;
+    int32_t tok[8];
+    if (tile < total_tiles) load_tokens(tile, tok);
+    while (ok && tile < total_tiles) {
+      // The next tile's row -> token table is fetched while this tile is gathered.
+      const int32_t next = tile + static_cast<int32_t>(gridDim.x);
+      int32_t tok_next[8];
+      if (next < total_tiles) load_tokens(next, tok_next);
       const int32_t rb = tile / p.num_slices;
-      if (p.row_offsets[rb] == p.row_offsets[rb + 1]) continue;
-      const int32_t token = p.row_token[static_cast<int64_t>(rb) * Cfg::kTileM + r];
-      const bool real = token >= 0;
-      // Padding rows still pass a valid address; the zero-fill form reads nothing from it.
-      const __nv_bfloat16* src = p.x + (real ? static_cast<int64_t>(token) * p.d_model : 0);
-      const int32_t k_steps = p.d_model / Cfg::kTileK;
-      for (int32_t ks = 0; ks < k_steps; ++ks) {
-        if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
-          give_up(SB_DEV_TIMEOUT_PRODUCER);
-          ok = false;
-          break;
-        }
-        const uint32_t dst = a_base + stage * Cfg::kABytes + row_dst;
-        const __nv_bfloat16* s = src + ks * Cfg::kTileK;
+      if (p.row_offsets[rb] != p.row_offsets[rb + 1]) {
+        const __nv_bfloat16* src[8];
 #pragma unroll
-        for (uint32_t c = 0; c < 8; ++c) ptx::cp_async_16_zfill(dst + ((c ^ swz) << 4), s + c * 8, real);
-        ptx::cp_async_mbar_arrive_noinc(full_bar + 8 * stage);
-        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        for (int j = 0; j < 8; ++j) {
+          // Padding rows still pass a valid address; the zero-fill form reads nothing from it.
+          src[j] = p.x + (tok[j] >= 0 ? static_cast<int64_t>(tok[j]) * p.d_model : 0) + chunk * 8;
+        }
+        const int32_t k_steps = p.d_model / Cfg::kTileK;
+        for (int32_t ks = 0; ks < k_steps; ++ks) {
+          if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
+            give_up(SB_DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t dst = a_base + stage * Cfg::kABytes + dst_off;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            ptx::cp_async_16_zfill(dst + j * 2048, src[j] + ks * Cfg::kTileK, tok[j] >= 0);
+          ptx::cp_async_mbar_arrive_noinc(full_bar + 8 * stage);
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tok[j] = tok_next[j];
+      tile = next;
     }
     ptx::cp_async_wait_all();
   }

@@ -32,7 +32,6 @@ constexpr int kSingleCtaThreads = 1024;
 constexpr int kChunkThreads = 256;
 constexpr int kChunkWarps = kChunkThreads / 32;
 constexpr int kChunkCopies = 2048;  // copies per block in the large shape
-constexpr int kLayoutThreads = 256;
 
 template <typename index_t>
 __device__ __forceinline__ int32_t read_expert(const index_t* __restrict__ expert_idx, int64_t c, int64_t end,
@@ -44,13 +43,25 @@ __device__ __forceinline__ int32_t read_expert(const index_t* __restrict__ exper
   return -1;
 }
 
-// One warp adds its run [begin, end) to its private counters. Returns true if it saw a bad id.
-template <typename index_t>
-__device__ bool warp_count_run(const index_t* __restrict__ expert_idx, int64_t begin, int64_t end,
-                               int32_t num_experts, int32_t* counters, int lane) {
+// A warp's run of copies is read up front, kIters x 32 ids into registers, so that the loads are all
+// in flight together instead of one memory latency per step. Returns true if a bad id was seen.
+template <typename index_t, int kIters>
+__device__ __forceinline__ bool load_run(const index_t* __restrict__ expert_idx, int64_t begin, int64_t end,
+                                         int32_t num_experts, int lane, int32_t (&ids)[kIters]) {
   bool bad = false;
-  for (int64_t c0 = begin; c0 < end; c0 += 32) {
-    const int32_t e = read_expert(expert_idx, c0 + lane, end, num_experts, bad);
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) ids[it] = read_expert(expert_idx, begin + it * 32 + lane, end, num_experts, bad);
+  return bad;
+}
+
+// One warp adds its run to its private counters, 32 copies per step in copy order.
+template <int kIters>
+__device__ __forceinline__ void count_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t* counters,
+                                          int lane) {
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    if (begin + it * 32 >= end) break;  // uniform across the warp
+    const int32_t e = ids[it];
     const bool valid = e >= 0;
     const unsigned active = __ballot_sync(kFullMask, valid);
     if (valid) {
@@ -59,20 +70,20 @@ __device__ bool warp_count_run(const index_t* __restrict__ expert_idx, int64_t b
     }
     __syncwarp();
   }
-  return bad;
 }
 
 // One warp places its run. counters[e] holds the number of copies of e that come before this run
 // (all earlier chunks and warps) and is advanced as the run is walked.
-template <typename index_t>
-__device__ void warp_scatter_run(const index_t* __restrict__ expert_idx, int64_t begin, int64_t end,
-                                 int32_t num_experts, int32_t k, int32_t* counters,
-                                 const int32_t* padded_offsets, int32_t* __restrict__ copy_row,
-                                 int32_t* __restrict__ row_token, int lane) {
-  bool bad = false;
-  for (int64_t c0 = begin; c0 < end; c0 += 32) {
-    const int64_t c = c0 + lane;
-    const int32_t e = read_expert(expert_idx, c, end, num_experts, bad);
+template <int kIters>
+__device__ __forceinline__ void scatter_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t k,
+                                            int32_t* counters, const int32_t* padded_offsets,
+                                            int32_t* __restrict__ copy_row, int32_t* __restrict__ row_token,
+                                            int lane) {
+#pragma unroll
+  for (int it = 0; it < kIters; ++it) {
+    if (begin + it * 32 >= end) break;  // uniform across the warp
+    const int64_t c = begin + it * 32 + lane;
+    const int32_t e = ids[it];
     const bool valid = e >= 0;
     const unsigned active = __ballot_sync(kFullMask, valid);
     unsigned peers = 0, lower = 0;
@@ -88,9 +99,9 @@ __device__ void warp_scatter_run(const index_t* __restrict__ expert_idx, int64_t
     if (valid) {
       const int32_t row = padded_offsets[e] + before + __popc(lower);
       copy_row[c] = row;
-      row_token[row] = static_cast<int32_t>(c / k);
+      row_token[row] = static_cast<int32_t>(static_cast<uint32_t>(c) / static_cast<uint32_t>(k));
     } else if (c < end) {
-      copy_row[c] = -1;
+      copy_row[c] = -1;  // bad id: skipped
     }
   }
 }
@@ -166,7 +177,7 @@ __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32
 // ---------------------------------------------------------------------------------------------
 // Small shape: everything in one block.
 // Shared memory: counters[32][E] | offsets[E+1] | counts[E] | warp_sums[32].
-template <typename index_t>
+template <typename index_t, int kIters>
 __global__ void __launch_bounds__(kSingleCtaThreads, 1)
 route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t k, int32_t num_experts,
                           int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
@@ -181,14 +192,16 @@ route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < kWarps * num_experts; i += kSingleCtaThreads) counters[i] = 0;
-  __syncthreads();
 
-  // Runs of equal length, a multiple of 32, in copy order.
+  // Runs of equal length, a multiple of 32 and at most kIters * 32, in copy order.
   const int64_t run = static_cast<int64_t>((n + kSingleCtaThreads - 1) / kSingleCtaThreads) * 32;
   const int64_t begin = min(static_cast<int64_t>(n), warp * run);
   const int64_t end = min(static_cast<int64_t>(n), begin + run);
-  const bool bad = warp_count_run(expert_idx, begin, end, num_experts, counters + warp * num_experts, lane);
+  int32_t ids[kIters];
+  const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
+  for (int i = threadIdx.x; i < kWarps * num_experts; i += kSingleCtaThreads) counters[i] = 0;
+  __syncthreads();
+  count_run<kIters>(ids, begin, end, counters + warp * num_experts, lane);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) error[0] = any_bad ? 1 : 0;
 
@@ -218,8 +231,7 @@ route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int
   }
   __syncthreads();
 
-  warp_scatter_run(expert_idx, begin, end, num_experts, k, counters + warp * num_experts, offsets, copy_row,
-                   layout.row_token, lane);
+  scatter_run<kIters>(ids, begin, end, k, counters + warp * num_experts, offsets, copy_row, layout.row_token, lane);
   fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, warp, kWarps, lane);
 }
 
@@ -236,9 +248,12 @@ route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int3
   __syncthreads();
 
   constexpr int64_t kRun = kChunkCopies / kChunkWarps;
+  constexpr int kIters = static_cast<int>(kRun / 32);
   const int64_t begin = min(n, static_cast<int64_t>(blockIdx.x) * kChunkCopies + warp * kRun);
   const int64_t end = min(n, begin + kRun);
-  const bool bad = warp_count_run(expert_idx, begin, end, num_experts, smem + warp * num_experts, lane);
+  int32_t ids[kIters];
+  const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
+  count_run<kIters>(ids, begin, end, smem + warp * num_experts, lane);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) chunk_error[blockIdx.x] = any_bad;
 
@@ -302,12 +317,15 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
     return;
   }
 
-  for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
-  __syncthreads();
   constexpr int64_t kRun = kChunkCopies / kChunkWarps;
+  constexpr int kIters = static_cast<int>(kRun / 32);
   const int64_t begin = min(n, static_cast<int64_t>(blockIdx.x) * kChunkCopies + warp * kRun);
   const int64_t end = min(n, begin + kRun);
-  warp_count_run(expert_idx, begin, end, num_experts, smem + warp * num_experts, lane);
+  int32_t ids[kIters];
+  load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
+  for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
+  __syncthreads();
+  count_run<kIters>(ids, begin, end, smem + warp * num_experts, lane);
   __syncthreads();
   const int32_t* base = chunk_base + static_cast<int64_t>(blockIdx.x) * num_experts;
   for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
@@ -321,8 +339,7 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
     }
   }
   __syncthreads();
-  warp_scatter_run(expert_idx, begin, end, num_experts, k, smem + warp * num_experts, padded_offsets, copy_row,
-                   layout.row_token, lane);
+  scatter_run<kIters>(ids, begin, end, k, smem + warp * num_experts, padded_offsets, copy_row, layout.row_token, lane);
 }
 
 size_t single_block_smem_bytes(int32_t num_experts) {
@@ -341,18 +358,27 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   if (info == nullptr) return SB_ERR_CUDA;
 
   if (n <= kSingleCtaMaxCopies) {
-    static bool attr_done[kMaxDevices] = {};
     const size_t smem = single_block_smem_bytes(num_experts);
-    if (!attr_done[device]) {
-      const cudaError_t err = cudaFuncSetAttribute(route_single_block_kernel<index_t>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   static_cast<int>(single_block_smem_bytes(kMaxExperts)));
-      if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
-      attr_done[device] = true;
-    }
-    route_single_block_kernel<index_t><<<1, kSingleCtaThreads, smem, stream>>>(
-        expert_idx, static_cast<int32_t>(n), k, num_experts, ffn_blocks, block_size, max_row_blocks,
-        tokens_per_expert, padded_offsets, copy_row, layout, error);
+    const int32_t n32 = static_cast<int32_t>(n);
+    auto launch = [&](auto kernel, bool* attr_done) -> int {
+      if (!attr_done[device]) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(single_block_smem_bytes(kMaxExperts)));
+        if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
+        attr_done[device] = true;
+      }
+      kernel<<<1, kSingleCtaThreads, smem, stream>>>(expert_idx, n32, k, num_experts, ffn_blocks, block_size,
+                                                     max_row_blocks, tokens_per_expert, padded_offsets, copy_row,
+                                                     layout, error);
+      return SB_OK;
+    };
+    // Copies per warp = ceil(n / 1024) * 32; the kernel keeps them in kIters registers per thread.
+    static bool done8[kMaxDevices] = {}, done16[kMaxDevices] = {}, done32[kMaxDevices] = {};
+    int rc;
+    if (n <= 8 * kSingleCtaThreads) rc = launch(route_single_block_kernel<index_t, 8>, done8);
+    else if (n <= 16 * kSingleCtaThreads) rc = launch(route_single_block_kernel<index_t, 16>, done16);
+    else rc = launch(route_single_block_kernel<index_t, 32>, done32);
+    if (rc != SB_OK) return rc;
     return check_launch("routing (single block)");
   }
 
