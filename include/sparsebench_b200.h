@@ -6,8 +6,8 @@
  *   - only enqueues work on that stream: it never synchronises, never reads device memory back
  *     to the host and never calls cudaMalloc/cudaFree (all buffers belong to the caller),
  *   - works on the calling thread's current CUDA device,
- *   - returns SB_OK (0) or a negative-free small positive status code; sb_last_error() gives the
- *     text for the calling thread's last failure.
+ *   - returns SB_OK (0) or one of the sb_status codes; sb_last_error() gives the text of the
+ *     calling thread's last failure.
  *
  * Buffers are sized for the worst case on the host; the real padded row count stays in
  * padded_offsets[num_experts] on the device and the kernels read it (or the flat tail of
@@ -85,7 +85,9 @@ size_t sb_route_workspace_bytes(int64_t n_copies, int32_t num_experts);
  *   col_indices[]      = expert * ffn_blocks + j, -1 past the real end
  *   error[0]           = 1 if any expert id was out of range, else 0 (written, not OR-ed)
  * expert_idx is int32 (idx_is_i64 == 0) or int64. workspace must hold
- * sb_route_workspace_bytes() bytes (may be NULL when that is 0).
+ * sb_route_workspace_bytes() bytes (may be NULL when that is 0). A caller that only wants the sort
+ * (the expert-parallel dispatch, at block_size 1) passes NULL for row_block_expert, row_offsets
+ * and col_indices together; those three arrays are then not produced.
  */
 int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k, int32_t num_experts,
              int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
@@ -157,6 +159,45 @@ int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_ro
  */
 int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gate_dtype, void* out,
                int64_t num_tokens, int32_t k, int32_t d_model, sb_stream_t stream);
+
+/*
+ * ---- Expert-parallel plumbing (no counterpart in the reference, which is single-GPU) ----------
+ *
+ * N ranks, E experts in total, rank d owns experts [d*experts_per_rank, (d+1)*experts_per_rank).
+ * A rank first sorts its n copies by GLOBAL expert with sb_route at block_size 1 (no padding):
+ * padded_offsets then is the exclusive scan of the per-expert counts, row_token the source token
+ * of every sorted position, copy_row the sorted position of every copy. Exchange buffers have a
+ * fixed capacity of `capacity` rows per (source, destination) pair, so no size depends on a count
+ * the host does not know. The exchanges themselves are all-to-alls of the caller's choosing (NCCL).
+ */
+enum sb_ep_status { SB_EP_OK = 0, SB_EP_OVERFLOW = 1 /* a pair's run exceeded `capacity`: copies dropped */ };
+
+/*
+ * send_index[d*capacity + i] = source token of the i-th copy bound for rank d, -1 past the run;
+ * return_row[c] = d*capacity + i, the slot in which copy c's result comes back, -1 if it was
+ * dropped (overflow, or an expert id the sort rejected). status is OR-ed with SB_EP_OVERFLOW.
+ */
+int sb_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_token, const int32_t* copy_pos,
+               int64_t n_copies, int32_t num_ranks, int32_t experts_per_rank, int32_t capacity,
+               int32_t* send_index, int32_t* return_row, int32_t* status, sb_stream_t stream);
+
+/*
+ * recv_counts[s*experts_per_rank + e] = copies rank s sent for local expert e (its slice of
+ * tokens_per_expert after the count all-to-all). slot_expert[s*capacity + i] = local expert of
+ * receive slot (s, i), -1 past what rank s sent. Feeding slot_expert to sb_route as a k = 1
+ * problem gives the owner's layout; -1 slots are skipped by it (its error flag then only says
+ * that empty slots exist).
+ */
+int sb_ep_slot_experts(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_per_rank, int32_t capacity,
+                       int32_t* slot_expert, sb_stream_t stream);
+
+/*
+ * out[j][:] = src[index[j]][:] for every j in [0, num_out_rows) with index[j] >= 0; other rows of
+ * out are left untouched. row_bytes % 16 == 0, both buffers 16-byte aligned. Packs the dispatch
+ * buffer (src = x, index = send_index) and the return buffer (src = y, index = the owner's copy_row).
+ */
+int sb_gather_rows(const void* src, const int32_t* index, void* out, int64_t num_out_rows, int32_t row_bytes,
+                   sb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -186,3 +186,75 @@ def combine_cuda(y: torch.Tensor, copy_row: torch.Tensor, expert_weight: torch.T
                                       int(expert_weight.dtype == torch.float32), _ptr(out), num_tokens, k,
                                       y.shape[1], _stream()))
     return out
+
+
+# ---- expert-parallel plumbing (no counterpart in the reference's extension) ----------------------
+
+def sort_copies_cuda(expert_idx: torch.Tensor, num_experts: int) -> list[torch.Tensor]:
+    """Stable sort of the T*k copies by expert, nothing else: sb_route at block size 1 without the BSR
+    arrays. Returns [tokens_per_expert[E], offsets[E+1] (exclusive scan of the counts),
+    sorted_token[T*k] (-1 past the kept copies), copy_pos[T*k] (-1 for a rejected id), error[1]]."""
+    lib = _lib.load()
+    _check(expert_idx.is_cuda and expert_idx.dim() == 2 and expert_idx.is_contiguous() and
+           expert_idx.dtype in (torch.int32, torch.int64), "expert_idx must be a contiguous [T, k] int32/int64 CUDA tensor")
+    n, k = expert_idx.numel(), expert_idx.shape[1]
+    _check(n > 0, "expert_idx must be [T, k] with T, k > 0")
+    max_rb = ctypes.c_int64()
+    _lib.check(lib.sb_route_sizes(n, num_experts, 1, 1, ctypes.byref(max_rb), None, None))
+    work_ints = (lib.sb_route_workspace_bytes(n, num_experts) + 3) // 4
+    with torch.cuda.device(expert_idx.device):
+        sizes = [num_experts, num_experts + 1, n, n, 1, work_ints]
+        parts = list(torch.split(torch.empty(sum(sizes), dtype=torch.int32, device=expert_idx.device), sizes))
+        work = parts.pop()
+        counts, offsets, sorted_token, copy_pos, error = parts
+        _lib.check(lib.sb_route(_ptr(expert_idx), int(expert_idx.dtype == torch.int64), n, k, num_experts, 1, 1,
+                                max_rb.value, _ptr(counts), _ptr(offsets), _ptr(sorted_token), _ptr(copy_pos),
+                                None, None, None, _ptr(error), _ptr(work), _stream()))
+    return parts
+
+
+def ep_plan(expert_offsets: torch.Tensor, sorted_token: torch.Tensor, copy_pos: torch.Tensor, num_ranks: int,
+            experts_per_rank: int, capacity: int, status: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(send_index [N*C], return_row [n]) from a rank's block-size-1 sort by global expert."""
+    lib = _lib.load()
+    for t, name in ((expert_offsets, "expert_offsets"), (sorted_token, "sorted_token"), (copy_pos, "copy_pos"),
+                    (status, "status")):
+        _check_index(t, name)
+    _check(expert_offsets.numel() == num_ranks * experts_per_rank + 1, "expert_offsets must have E + 1 entries")
+    n = copy_pos.numel()
+    with torch.cuda.device(copy_pos.device):
+        send_index = torch.empty(num_ranks * capacity, dtype=torch.int32, device=copy_pos.device)
+        return_row = torch.empty(n, dtype=torch.int32, device=copy_pos.device)
+        _lib.check(lib.sb_ep_plan(_ptr(expert_offsets), _ptr(sorted_token), _ptr(copy_pos), n, num_ranks,
+                                  experts_per_rank, capacity, _ptr(send_index), _ptr(return_row), _ptr(status),
+                                  _stream()))
+    return send_index, return_row
+
+
+def ep_slot_experts(recv_counts: torch.Tensor, capacity: int) -> torch.Tensor:
+    """recv_counts [N, E_local] int32 -> slot_expert [N*capacity] int32 (-1 for empty slots)."""
+    lib = _lib.load()
+    _check(recv_counts.is_cuda and recv_counts.dtype == torch.int32 and recv_counts.dim() == 2 and
+           recv_counts.is_contiguous(), "recv_counts must be a contiguous [N, E_local] int32 CUDA tensor")
+    num_ranks, experts_per_rank = recv_counts.shape
+    with torch.cuda.device(recv_counts.device):
+        out = torch.empty(num_ranks * capacity, dtype=torch.int32, device=recv_counts.device)
+        _lib.check(lib.sb_ep_slot_experts(_ptr(recv_counts), num_ranks, experts_per_rank, capacity, _ptr(out), _stream()))
+    return out
+
+
+def gather_rows(src: torch.Tensor, index: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[j] = src[index[j]] where index[j] >= 0; other rows keep what they held."""
+    lib = _lib.load()
+    _check(src.is_cuda and src.dim() == 2 and src.is_contiguous(), "src must be a contiguous 2-D CUDA tensor")
+    _check_index(index, "index")
+    row_bytes = src.shape[1] * src.element_size()
+    _check(row_bytes % 16 == 0, f"row size ({row_bytes} bytes) must be a multiple of 16")
+    with torch.cuda.device(src.device):
+        if out is None:
+            out = torch.empty((index.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
+        _check(out.is_contiguous() and out.shape == (index.numel(), src.shape[1]) and out.dtype == src.dtype,
+               "out must be a contiguous [len(index), row] tensor of src's dtype")
+        if index.numel() > 0:
+            _lib.check(lib.sb_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), row_bytes, _stream()))
+    return out

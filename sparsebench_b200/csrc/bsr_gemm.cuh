@@ -140,6 +140,9 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
+      // Weights and H blocks are each read once per launch: mark them first to go, so that the
+      // streaming weights do not push H (written by SDD, read back by DSD) or x out of the L2.
+      const uint64_t stream_once = ptx::policy_evict_first();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
@@ -166,7 +169,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           } else {
             const int32_t blk = begin + (ks >> 1);
             const int32_t k_half = (ks & 1) * Cfg::kTileK;
-            ptx::tma_load_2d(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * Cfg::kTileM, bar);
+            ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * Cfg::kTileM, bar, stream_once);
             if ((ks & 1) == 0) {
               // The next block's column index is fetched one block ahead to keep it off the issue path.
               col_block = col_block_next;
@@ -177,7 +180,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t b_dst = b_base + stage * Cfg::kBBytes;
 #pragma unroll
           for (int j = 0; j < Cfg::kBSlabs; ++j)
-            ptx::tma_load_2d(b_dst + j * Cfg::kBSlabBytes, &map_b, n0 + j * 64, b_row, bar);
+            ptx::tma_load_2d_hint(b_dst + j * Cfg::kBSlabBytes, &map_b, n0 + j * 64, b_row, bar, stream_once);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
       }

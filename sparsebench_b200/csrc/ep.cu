@@ -1,0 +1,174 @@
+// Expert-parallel plumbing kernels: everything between the local sort of a rank's copies and the
+// all-to-all exchanges, kept on the device so that the step stays free of host syncs.
+//
+// Setting: N ranks, E experts in total, rank d owns experts [d*Epr, (d+1)*Epr). A rank sorts its
+// n = T*k copies by GLOBAL expert id with the routing kernel at block_size 1 (no padding), which
+// makes the copies bound for rank d one contiguous run [off_d, off_d + cnt_d) of sorted positions.
+// Exchange buffers have a fixed capacity of C rows per (source, destination) pair, so their size
+// never depends on a count the host does not know:
+//   send[d][i]   i-th copy bound for rank d      recv[s][i]   i-th copy received from rank s
+// The owner treats its N*C receive slots as "tokens" of a local k = 1 routing problem; slots past
+// the received count carry expert id -1 and are skipped by the routing kernel.
+//
+// sb_ep_plan         send_index[d*C+i] = source token of slot (d, i) or -1;
+//                    return_row[c] = slot d*C+i in which copy c's result comes back, or -1 if the
+//                    pair's run overflowed C (then status |= SB_EP_OVERFLOW).
+// sb_ep_slot_experts slot_expert[s*C+i] = local expert of the i-th copy from rank s, or -1.
+// sb_gather_rows     out[j][:] = src[index[j]][:] where index[j] >= 0 (16-byte vectors).
+
+#include <cuda_bf16.h>
+
+#include "sb_common.cuh"
+
+namespace sb {
+namespace {
+
+constexpr int kThreads = 256;
+
+// Rank whose run contains sorted position `pos`: the last d with rank_start(d) <= pos.
+__device__ __forceinline__ int owner_of(const int32_t* __restrict__ expert_offsets, int32_t experts_per_rank,
+                                        int32_t num_ranks, int32_t pos) {
+  int lo = 0, hi = num_ranks - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (expert_offsets[mid * experts_per_rank] <= pos) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kThreads)
+ep_plan_kernel(const int32_t* __restrict__ expert_offsets, const int32_t* __restrict__ sorted_token,
+               const int32_t* __restrict__ copy_pos, int32_t n_copies, int32_t num_ranks, int32_t experts_per_rank,
+               int32_t capacity, int32_t* __restrict__ send_index, int32_t* __restrict__ return_row,
+               int32_t* __restrict__ status) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // Slots: which token fills slot (d, i).
+  const int64_t slots = static_cast<int64_t>(num_ranks) * capacity;
+  for (int64_t s = first; s < slots; s += stride) {
+    const int32_t d = static_cast<int32_t>(s / capacity);
+    const int32_t i = static_cast<int32_t>(s - static_cast<int64_t>(d) * capacity);
+    const int32_t begin = expert_offsets[d * experts_per_rank];
+    const int32_t end = expert_offsets[(d + 1) * experts_per_rank];
+    send_index[s] = i < end - begin ? sorted_token[begin + i] : -1;
+    if (i == 0 && end - begin > capacity) atomicOr(status, SB_EP_OVERFLOW);
+  }
+  // Copies: in which slot copy c's result returns. A copy the local sort skipped (bad id) has
+  // copy_pos < 0 and contributes nothing.
+  for (int64_t c = first; c < n_copies; c += stride) {
+    const int32_t pos = copy_pos[c];
+    int32_t slot = -1;
+    if (pos >= 0) {
+      const int d = owner_of(expert_offsets, experts_per_rank, num_ranks, pos);
+      const int32_t i = pos - expert_offsets[d * experts_per_rank];
+      if (i < capacity) slot = d * capacity + i;
+    }
+    return_row[c] = slot;
+  }
+}
+
+// grid = (ceil(C / kThreads), N). recv_counts[s][e] = copies rank s sent for local expert e.
+__global__ void __launch_bounds__(kThreads)
+ep_slot_experts_kernel(const int32_t* __restrict__ recv_counts, int32_t experts_per_rank, int32_t capacity,
+                       int32_t* __restrict__ slot_expert) {
+  extern __shared__ int32_t ends[];  // inclusive prefix of this source's counts, [experts_per_rank]
+  const int32_t s = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int32_t running = 0;
+    for (int32_t e = 0; e < experts_per_rank; ++e) {
+      running += max(0, recv_counts[s * experts_per_rank + e]);
+      ends[e] = running;
+    }
+  }
+  __syncthreads();
+  const int32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= capacity) return;
+  int32_t expert = -1;
+  if (i < ends[experts_per_rank - 1]) {
+    int32_t lo = 0, hi = experts_per_rank - 1;  // first e with ends[e] > i
+    while (lo < hi) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (ends[mid] > i) hi = mid; else lo = mid + 1;
+    }
+    expert = lo;
+  }
+  slot_expert[static_cast<int64_t>(s) * capacity + i] = expert;
+}
+
+// One warp per output row; lanes copy 16-byte vectors.
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, uint4* __restrict__ out,
+                   int64_t num_out_rows, int32_t vecs_per_row) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); j < num_out_rows;
+       j += warps) {
+    const int32_t row = __ldg(index + j);
+    if (row < 0) continue;
+    const uint4* s = src + static_cast<int64_t>(row) * vecs_per_row;
+    uint4* d = out + j * vecs_per_row;
+    for (int32_t v = lane; v < vecs_per_row; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+int64_t capped_blocks(int64_t items, int per_block, const DeviceInfo* info) {
+  int64_t blocks = (items + per_block - 1) / per_block;
+  const int64_t cap = static_cast<int64_t>(info->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : blocks;
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" {
+
+int sb_ep_plan(const int32_t* expert_offsets, const int32_t* sorted_token, const int32_t* copy_pos,
+               int64_t n_copies, int32_t num_ranks, int32_t experts_per_rank, int32_t capacity,
+               int32_t* send_index, int32_t* return_row, int32_t* status, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!expert_offsets || !sorted_token || !copy_pos || !send_index || !return_row || !status)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_plan: NULL buffer");
+  if (n_copies <= 0 || n_copies > INT32_MAX || num_ranks <= 0 || experts_per_rank <= 0 || capacity <= 0 ||
+      static_cast<int64_t>(num_ranks) * capacity > INT32_MAX)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_plan: sizes must be positive and fit int32");
+  const DeviceInfo* info = current_device_info();
+  if (info == nullptr) return SB_ERR_CUDA;
+  const int64_t items = std::max<int64_t>(n_copies, static_cast<int64_t>(num_ranks) * capacity);
+  ep_plan_kernel<<<static_cast<unsigned>(capped_blocks(items, kThreads, info)), kThreads, 0, as_stream(stream)>>>(
+      expert_offsets, sorted_token, copy_pos, static_cast<int32_t>(n_copies), num_ranks, experts_per_rank, capacity,
+      send_index, return_row, status);
+  return check_launch("ep_plan");
+}
+
+int sb_ep_slot_experts(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_per_rank, int32_t capacity,
+                       int32_t* slot_expert, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!recv_counts || !slot_expert) return fail(SB_ERR_INVALID_ARGUMENT, "ep_slot_experts: NULL buffer");
+  if (num_ranks <= 0 || num_ranks > 65535 || experts_per_rank <= 0 || experts_per_rank > 1024 || capacity <= 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_slot_experts: need 0 < ranks < 65536, 0 < experts per rank <= 1024");
+  const dim3 grid(static_cast<unsigned>((capacity + kThreads - 1) / kThreads), static_cast<unsigned>(num_ranks));
+  ep_slot_experts_kernel<<<grid, kThreads, experts_per_rank * sizeof(int32_t), as_stream(stream)>>>(
+      recv_counts, experts_per_rank, capacity, slot_expert);
+  return check_launch("ep_slot_experts");
+}
+
+int sb_gather_rows(const void* src, const int32_t* index, void* out, int64_t num_out_rows, int32_t row_bytes,
+                   sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!src || !index || !out) return fail(SB_ERR_INVALID_ARGUMENT, "gather_rows: NULL buffer");
+  if (num_out_rows <= 0 || row_bytes <= 0 || row_bytes % 16 != 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "gather_rows: row size (%d bytes) must be a positive multiple of 16", row_bytes);
+  if (!aligned16(src) || !aligned16(out)) return fail(SB_ERR_INVALID_ARGUMENT, "gather_rows: buffers must be 16-byte aligned");
+  const DeviceInfo* info = current_device_info();
+  if (info == nullptr) return SB_ERR_CUDA;
+  gather_rows_kernel<<<static_cast<unsigned>(capped_blocks(num_out_rows, kThreads / 32, info)), kThreads, 0,
+                       as_stream(stream)>>>(static_cast<const uint4*>(src), index, static_cast<uint4*>(out),
+                                            num_out_rows, row_bytes / 16);
+  return check_launch("gather_rows");
+}
+
+}  // extern "C"

@@ -54,53 +54,53 @@ __device__ __forceinline__ bool load_run(const index_t* __restrict__ expert_idx,
   return bad;
 }
 
-// One warp adds its run to its private counters, 32 copies per step in copy order.
+// One warp walks its run 32 copies per step, in copy order, and adds it to its private counters.
+// For every copy it also returns pos = the number of copies of the same expert that come earlier in
+// this run: __match_any_sync gives the lanes holding the same expert, the ones below count towards
+// pos, and the lowest of them alone reads and advances the counter (one writer per expert per step)
+// and hands the old value to its peers. Nothing here depends on timing, so the order is stable.
 template <int kIters>
-__device__ __forceinline__ void count_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t* counters,
-                                          int lane) {
+__device__ __forceinline__ void rank_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t* counters,
+                                         int lane, int32_t (&pos)[kIters]) {
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
-    if (begin + it * 32 >= end) break;  // uniform across the warp
+    pos[it] = 0;
+    if (begin + it * 32 >= end) continue;  // uniform across the warp
     const int32_t e = ids[it];
     const bool valid = e >= 0;
     const unsigned active = __ballot_sync(kFullMask, valid);
+    unsigned peers = 0;
+    int32_t before = 0;
     if (valid) {
-      const unsigned peers = __match_any_sync(active, e);
-      if ((peers & ((1u << lane) - 1u)) == 0) counters[e] += __popc(peers);  // one writer per expert
+      peers = __match_any_sync(active, e);
+      if ((peers & ((1u << lane) - 1u)) == 0) {
+        before = counters[e];
+        counters[e] = before + __popc(peers);
+      }
     }
+    const int leader = peers != 0 ? __ffs(peers) - 1 : lane;
+    before = __shfl_sync(kFullMask, before, leader);
+    pos[it] = before + __popc(peers & ((1u << lane) - 1u));
     __syncwarp();
   }
 }
 
-// One warp places its run. counters[e] holds the number of copies of e that come before this run
-// (all earlier chunks and warps) and is advanced as the run is walked.
+// Places a run. bases[e] = copies of expert e before this run (earlier chunks and warps).
 template <int kIters>
-__device__ __forceinline__ void scatter_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t k,
-                                            int32_t* counters, const int32_t* padded_offsets,
-                                            int32_t* __restrict__ copy_row, int32_t* __restrict__ row_token,
-                                            int lane) {
+__device__ __forceinline__ void scatter_run(const int32_t (&ids)[kIters], const int32_t (&pos)[kIters], int64_t begin,
+                                            int64_t end, int32_t k, const int32_t* bases,
+                                            const int32_t* padded_offsets, int32_t* __restrict__ copy_row,
+                                            int32_t* __restrict__ row_token, int lane) {
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
-    if (begin + it * 32 >= end) break;  // uniform across the warp
     const int64_t c = begin + it * 32 + lane;
+    if (c >= end) continue;
     const int32_t e = ids[it];
-    const bool valid = e >= 0;
-    const unsigned active = __ballot_sync(kFullMask, valid);
-    unsigned peers = 0, lower = 0;
-    int32_t before = 0;
-    if (valid) {
-      peers = __match_any_sync(active, e);
-      lower = peers & ((1u << lane) - 1u);
-      before = counters[e];
-    }
-    __syncwarp();
-    if (valid && lower == 0) counters[e] = before + __popc(peers);
-    __syncwarp();
-    if (valid) {
-      const int32_t row = padded_offsets[e] + before + __popc(lower);
+    if (e >= 0) {
+      const int32_t row = padded_offsets[e] + bases[e] + pos[it];
       copy_row[c] = row;
       row_token[row] = static_cast<int32_t>(static_cast<uint32_t>(c) / static_cast<uint32_t>(k));
-    } else if (c < end) {
+    } else {
       copy_row[c] = -1;  // bad id: skipped
     }
   }
@@ -140,11 +140,19 @@ struct LayoutOut {
 };
 
 // Fills every worst-case slot the scatter does not write. `warp_index` of `warp_count` warps share
-// the row blocks. offsets[E+1] and counts[E] may be in shared or global memory.
+// the row blocks. offsets[E+1] and counts[E] may be in shared or global memory. With null BSR
+// pointers (a caller that only wants the sort) just the -1 rows are written.
 __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32_t num_experts, int32_t block_size,
                             int32_t ffn_blocks, int32_t max_row_blocks, const LayoutOut& out, int warp_index,
                             int warp_count, int lane) {
   const int32_t num_row_blocks = offsets[num_experts] / block_size;
+  const bool want_bsr = out.col_indices != nullptr;
+  if (block_size == 1 && !want_bsr) {
+    // No padding inside an expert's group: only the rows past the real end are -1.
+    for (int32_t r = num_row_blocks + warp_index * 32 + lane; r < max_row_blocks; r += warp_count * 32)
+      out.row_token[r] = -1;
+    return;
+  }
   for (int32_t rb = warp_index; rb < max_row_blocks; rb += warp_count) {
     int32_t expert = -1;
     int32_t real_rows = 0;
@@ -163,6 +171,7 @@ __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32
     }
     const int64_t row_base = static_cast<int64_t>(rb) * block_size;
     for (int32_t j = real_rows + lane; j < block_size; j += 32) out.row_token[row_base + j] = -1;
+    if (!want_bsr) continue;
     const int64_t col_base = static_cast<int64_t>(rb) * ffn_blocks;
     for (int32_t j = lane; j < ffn_blocks; j += 32)
       out.col_indices[col_base + j] = expert < 0 ? -1 : expert * ffn_blocks + j;
@@ -171,7 +180,8 @@ __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32
       out.row_offsets[rb] = min(rb, num_row_blocks) * ffn_blocks;
     }
   }
-  if (warp_index == 0 && lane == 0) out.row_offsets[max_row_blocks] = min(max_row_blocks, num_row_blocks) * ffn_blocks;
+  if (want_bsr && warp_index == 0 && lane == 0)
+    out.row_offsets[max_row_blocks] = min(max_row_blocks, num_row_blocks) * ffn_blocks;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -201,23 +211,30 @@ route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int
   const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
   for (int i = threadIdx.x; i < kWarps * num_experts; i += kSingleCtaThreads) counters[i] = 0;
   __syncthreads();
-  count_run<kIters>(ids, begin, end, counters + warp * num_experts, lane);
+  int32_t pos[kIters];
+  rank_run<kIters>(ids, begin, end, counters + warp * num_experts, lane, pos);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) error[0] = any_bad ? 1 : 0;
 
-  // Per expert: exclusive scan over the warps (in place), total = copies of that expert.
-  int32_t total = 0;
-  const int e = threadIdx.x;
-  if (e < num_experts) {
-    for (int w = 0; w < kWarps; ++w) {
-      int32_t* slot = counters + w * num_experts + e;
-      const int32_t c = *slot;
-      *slot = total;
-      total += c;
+  // Per expert: exclusive scan of the 32 warps' counters, in place. Warp w takes experts w, w + 32,
+  // ...; lane l holds the counter of warp l, so the scan is five shuffles instead of 32 serial steps.
+  for (int e = warp; e < num_experts; e += kWarps) {
+    int32_t* slot = counters + lane * num_experts + e;
+    const int32_t mine = *slot;
+    int32_t inclusive = mine;
+    for (int d = 1; d < 32; d <<= 1) {
+      const int32_t below = __shfl_up_sync(kFullMask, inclusive, d);
+      if (lane >= d) inclusive += below;
     }
-    counts[e] = total;
-    tokens_per_expert[e] = total;
+    *slot = inclusive - mine;
+    if (lane == 31) {
+      counts[e] = inclusive;
+      tokens_per_expert[e] = inclusive;
+    }
   }
+  __syncthreads();
+  const int e = threadIdx.x;
+  const int32_t total = e < num_experts ? counts[e] : 0;
   const int32_t padded = e < num_experts ? (total + block_size - 1) / block_size * block_size : 0;
   int32_t all_rows = 0;
   const int32_t start = block_exclusive_scan(padded, warp_sums, &all_rows);
@@ -231,7 +248,8 @@ route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int
   }
   __syncthreads();
 
-  scatter_run<kIters>(ids, begin, end, k, counters + warp * num_experts, offsets, copy_row, layout.row_token, lane);
+  scatter_run<kIters>(ids, pos, begin, end, k, counters + warp * num_experts, offsets, copy_row, layout.row_token,
+                      lane);
   fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, warp, kWarps, lane);
 }
 
@@ -253,7 +271,8 @@ route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int3
   const int64_t end = min(n, begin + kRun);
   int32_t ids[kIters];
   const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
-  count_run<kIters>(ids, begin, end, smem + warp * num_experts, lane);
+  int32_t pos[kIters];
+  rank_run<kIters>(ids, begin, end, smem + warp * num_experts, lane, pos);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) chunk_error[blockIdx.x] = any_bad;
 
@@ -325,7 +344,8 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
   load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
   for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
   __syncthreads();
-  count_run<kIters>(ids, begin, end, smem + warp * num_experts, lane);
+  int32_t pos[kIters];
+  rank_run<kIters>(ids, begin, end, smem + warp * num_experts, lane, pos);
   __syncthreads();
   const int32_t* base = chunk_base + static_cast<int64_t>(blockIdx.x) * num_experts;
   for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
@@ -339,7 +359,8 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
     }
   }
   __syncthreads();
-  scatter_run<kIters>(ids, begin, end, k, smem + warp * num_experts, padded_offsets, copy_row, layout.row_token, lane);
+  scatter_run<kIters>(ids, pos, begin, end, k, smem + warp * num_experts, padded_offsets, copy_row, layout.row_token,
+                      lane);
 }
 
 size_t single_block_smem_bytes(int32_t num_experts) {
@@ -481,9 +502,12 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
   if (want_rb != max_row_blocks)
     return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: max_row_blocks is %d, worst case needs %lld", max_row_blocks,
                     (long long)want_rb);
-  if (!expert_idx || !tokens_per_expert || !padded_offsets || !row_token || !copy_row || !row_block_expert ||
-      !row_offsets || !col_indices || !error)
+  if (!expert_idx || !tokens_per_expert || !padded_offsets || !row_token || !copy_row || !error)
     return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: NULL buffer");
+  const int bsr_given = (row_block_expert != nullptr) + (row_offsets != nullptr) + (col_indices != nullptr);
+  if (bsr_given != 0 && bsr_given != 3)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT,
+                    "routing: row_block_expert, row_offsets and col_indices must be all given or all NULL");
   if (workspace == nullptr && sb_route_workspace_bytes(n_copies, num_experts) != 0)
     return sb::fail(SB_ERR_INVALID_ARGUMENT, "routing: workspace is NULL but %zu bytes are needed",
                     sb_route_workspace_bytes(n_copies, num_experts));

@@ -1,0 +1,185 @@
+"""The expert-parallel arm of bench.py: one rank per GPU under torchrun (or a single process for
+world size 1). Weak scaling: every rank brings T tokens, the E experts are split over the ranks.
+
+Timing: CUDA events around every step on the launching stream, 256 MiB written before every step
+to flush L2, a barrier and a device synchronise on both sides of the timed region, per-rank sums
+reduced with MAX. The step is one CUDA-graph replay when the collectives can be captured, else
+eager launches (config.launch says which).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from sparsebench_b200.ep import ExpertParallelMoE
+from sparsebench_b200.timing import l2_flush_buffer
+from sparsebench_b200.workloads import CONFIGS, make_layer
+
+NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool; 900 nominal
+
+
+def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int) -> float:
+    """Mean ms per step, max over ranks."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(steps):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        step()
+        end.record()
+        pairs.append((start, end))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    total = torch.tensor([sum(s.elapsed_time(e) for s, e in pairs)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    return float(total.item()) / steps
+
+
+def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -> None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = CONFIGS[args.workload or "expert_parallel"]
+    if cfg.num_experts % world != 0:
+        raise SystemExit(f"{cfg.num_experts} experts do not split over {world} ranks")
+    per_rank = cfg.num_experts // world
+    mine = range(rank * per_rank, (rank + 1) * per_rank)
+    layer_in = make_layer(cfg, seed=0, token_seed=rank, experts=mine)
+    dev = layer_in.to(device)
+    moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts)
+    flush = l2_flush_buffer(device)
+    hbm_gbs, bf16_tflops, peak_kind = peaks
+
+    out = moe(dev.x, dev.expert_idx, dev.expert_weight)
+    torch.cuda.synchronize()
+    moe.check()
+
+    # ---- value: graph replay if the collectives capture, else eager --------------------------------
+    launch = "eager launches (graph capture of the collectives was refused)"
+    step = lambda: moe(dev.x, dev.expert_idx, dev.expert_weight)  # noqa: E731
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            moe(dev.x, dev.expert_idx, dev.expert_weight)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = moe(dev.x, dev.expert_idx, dev.expert_weight)
+        graph.replay()
+        torch.cuda.synchronize()
+        if not torch.equal(graph_out, out):
+            raise RuntimeError("graph replay and eager launch disagree")
+        step, launch = graph.replay, "one CUDA-graph replay per step"
+    except RuntimeError as exc:
+        if "disagree" in str(exc):
+            raise
+        torch.cuda.synchronize()
+
+    with clock_sampler_cls(local) as clocks:
+        ms_per_step = _timed_steps(step, flush, args.warmup, args.steps, world)
+    value = world * cfg.useful_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- e2e: public API with host buffers -----------------------------------------------------------
+    host_x, host_idx, host_w = (t.pin_memory() for t in (layer_in.x, layer_in.expert_idx, layer_in.expert_weight))
+    host_out = torch.empty_like(layer_in.x).pin_memory()
+    dx, didx, dw = torch.empty_like(dev.x), torch.empty_like(dev.expert_idx), torch.empty_like(dev.expert_weight)
+
+    def e2e_step() -> None:
+        dx.copy_(host_x, non_blocking=True)
+        didx.copy_(host_idx, non_blocking=True)
+        dw.copy_(host_w, non_blocking=True)
+        host_out.copy_(moe(dx, didx, dw), non_blocking=True)
+
+    e2e_ms = _timed_steps(e2e_step, flush, args.warmup, args.steps, world)
+    h2d = sum(t.numel() * t.element_size() for t in (host_x, host_idx, host_w))
+    d2h = host_out.numel() * host_out.element_size()
+
+    # ---- per-stage times on this rank (eager, an event at every stage mark) ---------------------------
+    names: list[str] = []
+    sums: dict[str, float] = {}
+    iters = max(5, min(args.steps, 30))
+    for it in range(iters + 2):
+        flush.zero_()
+        events = [torch.cuda.Event(enable_timing=True)]
+        events[0].record()
+        seen: list[str] = []
+
+        def mark(stage: str) -> None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            events.append(ev)
+            seen.append(stage)
+
+        moe(dev.x, dev.expert_idx, dev.expert_weight, mark=mark)
+        torch.cuda.synchronize()
+        if it >= 2:
+            names = seen
+            for i, stage in enumerate(seen):
+                sums[stage] = sums.get(stage, 0.0) + events[i].elapsed_time(events[i + 1])
+    stage_ms = {s: sums[s] / iters for s in names}
+
+    rows = int(moe.last.owner_layout.padded_offsets[-1].item())  # live padded rows on this rank
+    received = int(moe.last.recv_counts.sum().item())
+    weight_bytes = per_rank * cfg.d_model * cfg.ffn_dim * 2
+    sdd_bytes = received * cfg.d_model * 2 + weight_bytes + rows * cfg.ffn_dim * 2
+    dsd_bytes = rows * cfg.ffn_dim * 2 + weight_bytes + rows * cfg.d_model * 2
+    gemm_ms = {"sdd": stage_ms["SDD + GELU (fused)"], "dsd": stage_ms["DSD"]}
+    gemm_bytes = {"sdd": sdd_bytes, "dsd": dsd_bytes}
+    dominant = max(gemm_ms, key=gemm_ms.get)
+    t_dom = gemm_ms[dominant] * 1e-3
+    exec_flops = 2 * rows * cfg.d_model * cfg.ffn_dim
+    if gemm_bytes[dominant] / (hbm_gbs * 1e9) >= exec_flops / (bf16_tflops * 1e12):
+        achieved = gemm_bytes[dominant] / t_dom / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs}
+    else:
+        achieved = exec_flops / t_dom / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_tflops, "unit": "TFLOP/s",
+                    "frac": achieved / bf16_tflops}
+    payload = (world - 1) / world * cfg.num_tokens * cfg.k * cfg.d_model * 2  # useful bytes per direction
+    roofline.update({
+        "kernel": f"bsr_gemm_kernel<{dominant}> on rank 0", "peak_source": peak_kind, "launch_ms": gemm_ms[dominant],
+        "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "traffic": None, "stages_ms": stage_ms,
+        "all_to_all": {"useful_bytes_per_direction": payload,
+                       "sent_bytes_per_direction": world * moe.capacity * cfg.d_model * 2,
+                       "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},
+    })
+
+    if rank == 0:
+        line = {
+            "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
+                       "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
+                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
+                       "launch": launch, "l2": "256 MiB written before every step",
+                       "frac_of_bf16_peak": value / world / bf16_tflops},
+            "clocks": clocks.summary(),
+            "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": (9 + (2 if world * moe.capacity > 32768 else 0)) * args.steps,
+            "roofline": roofline,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()

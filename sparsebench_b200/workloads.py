@@ -21,7 +21,8 @@ def _zipf_weights(num_experts: int) -> torch.Tensor:
     return 1.0 / ranks**ZIPF_EXPONENT
 
 
-def routing_case(name: str, num_tokens: int, num_experts: int, seed: int = 0) -> torch.Tensor:
+def routing_case(name: str, num_tokens: int, num_experts: int, seed: int = 0,
+                 perm_seed: int | None = None) -> torch.Tensor:
     """expert_idx [T, 2] int64 on the CPU, two different experts per token.
 
     random            two distinct experts uniformly
@@ -29,7 +30,9 @@ def routing_case(name: str, num_tokens: int, num_experts: int, seed: int = 0) ->
     two_experts_only  every token picks experts 0 and 1
     empty_middle      only experts 0 and E-1 are used (in a seeded order)
     zipf              expert popularity ~ 1 / rank^1.2, two distinct draws per token
-    permuted_zipf     zipf over a seeded random permutation of the experts
+    permuted_zipf     zipf over a seeded random permutation of the experts; `perm_seed` (default:
+                      `seed`) seeds the permutation alone, so that ranks with different tokens can
+                      share one popularity order
     """
     g = torch.Generator().manual_seed(seed)
     if name == "random":
@@ -45,7 +48,10 @@ def routing_case(name: str, num_tokens: int, num_experts: int, seed: int = 0) ->
     if name == "zipf":
         return torch.multinomial(_zipf_weights(num_experts).expand(num_tokens, -1), 2, replacement=False, generator=g)
     if name == "permuted_zipf":
-        perm = torch.randperm(num_experts, generator=g)
+        if perm_seed is None:
+            perm = torch.randperm(num_experts, generator=g)
+        else:
+            perm = torch.randperm(num_experts, generator=torch.Generator().manual_seed(perm_seed))
         picks = torch.multinomial(_zipf_weights(num_experts).expand(num_tokens, -1), 2, replacement=False, generator=g)
         return perm[picks]
     raise ValueError(name)
@@ -94,24 +100,28 @@ class LayerInputs:
         return LayerInputs(*(t.to(device) for t in (self.x, self.expert_idx, self.expert_weight, self.w1, self.w2)))
 
 
-def _weights(num_experts: int, rows: int, cols: int, g: torch.Generator, dtype: torch.dtype) -> torch.Tensor:
-    """[E, rows, cols] ~ N(0, 1/rows), generated one expert at a time to bound fp32 scratch."""
-    out = torch.empty(num_experts, rows, cols, dtype=dtype)
+def _weights(which: int, experts: range, rows: int, cols: int, seed: int, dtype: torch.dtype) -> torch.Tensor:
+    """[len(experts), rows, cols] ~ N(0, 1/rows). Every expert has its own generator, seeded by
+    (seed, expert, which), so a rank can generate just its slice and still agree with the others."""
+    out = torch.empty(len(experts), rows, cols, dtype=dtype)
     scale = rows**-0.5
-    for e in range(num_experts):
-        out[e] = (torch.randn(rows, cols, generator=g) * scale).to(dtype)
+    for slot, e in enumerate(experts):
+        g = torch.Generator().manual_seed(seed * 1_000_003 + 2 * e + which)
+        out[slot] = (torch.randn(rows, cols, generator=g) * scale).to(dtype)
     return out
 
 
 def make_layer(cfg: LayerConfig, seed: int = 0, dtype: torch.dtype = torch.bfloat16,
-               token_seed: int | None = None) -> LayerInputs:
+               token_seed: int | None = None, experts: range | None = None) -> LayerInputs:
     """CPU tensors for `cfg`: x ~ N(0,1), w1 ~ N(0,1/D), w2 ~ N(0,1/F) in `dtype`; expert choice by
     cfg.routing; gates = softmax of N(0,1) logits over the selected pair ("router": logits [T, E]
     ~ N(0,1), top-2 and softmax over the picks). `token_seed` (default = seed) seeds x, routing
-    and gates separately from the weights, for per-rank tokens over shared weights."""
-    g = torch.Generator().manual_seed(seed)
-    w1 = _weights(cfg.num_experts, cfg.d_model, cfg.ffn_dim, g, dtype)
-    w2 = _weights(cfg.num_experts, cfg.ffn_dim, cfg.d_model, g, dtype)
+    and gates separately from the weights, for per-rank tokens over shared weights (the Zipf
+    permutation stays seeded by `seed`). `experts` restricts w1/w2 to a slice of the experts
+    (expert ids in expert_idx stay global)."""
+    experts = range(cfg.num_experts) if experts is None else experts
+    w1 = _weights(0, experts, cfg.d_model, cfg.ffn_dim, seed, dtype)
+    w2 = _weights(1, experts, cfg.ffn_dim, cfg.d_model, seed, dtype)
     ts = seed if token_seed is None else token_seed
     gt = torch.Generator().manual_seed(1_000_003 + ts)
     x = torch.randn(cfg.num_tokens, cfg.d_model, generator=gt).to(dtype)
@@ -120,6 +130,6 @@ def make_layer(cfg: LayerConfig, seed: int = 0, dtype: torch.dtype = torch.bfloa
         picked, expert_idx = torch.topk(logits, cfg.k, dim=-1)
         gate = torch.softmax(picked, dim=-1)
     else:
-        expert_idx = routing_case(cfg.routing, cfg.num_tokens, cfg.num_experts, seed=ts)
+        expert_idx = routing_case(cfg.routing, cfg.num_tokens, cfg.num_experts, seed=ts, perm_seed=seed)
         gate = torch.softmax(torch.randn(cfg.num_tokens, cfg.k, generator=gt), dim=-1)
     return LayerInputs(x, expert_idx, gate.to(dtype), w1, w2)

@@ -1,0 +1,107 @@
+"""Expert-parallel plumbing kernels and the whole expert-parallel step on one GPU (world size 1:
+every all-to-all is the identity, every kernel of the step still runs). The multi-GPU run of the
+same step is tests/ep_multi_gpu.py, launched by torchrun."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import layout as L
+from oracle import moe as M
+from tests import ep_cpu_ops
+from tests.cases import routing_case
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize(("num_tokens", "num_experts", "ranks", "capacity"),
+                         [(300, 8, 2, 600), (300, 8, 4, 100), (4096, 128, 8, 8192), (20000, 64, 8, 40000)])
+def test_sort_and_plan_match_the_restatement(num_tokens: int, num_experts: int, ranks: int, capacity: int) -> None:
+    from sparsebench_b200 import _C
+
+    idx = routing_case("zipf", num_tokens, num_experts, seed=3)
+    counts, offsets, sorted_token, copy_pos, error = _C.sort_copies_cuda(idx.cuda(), num_experts)
+    expected = L.device_layout(idx, num_experts, 1, 1)
+    assert np.array_equal(counts.cpu().numpy(), expected.tokens_per_expert)
+    assert np.array_equal(offsets.cpu().numpy(), expected.padded_offsets)
+    assert np.array_equal(sorted_token.cpu().numpy(), expected.row_token)
+    assert np.array_equal(copy_pos.cpu().numpy(), expected.copy_row)
+    assert int(error.item()) == 0
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    per_rank = num_experts // ranks
+    send_index, return_row = _C.ep_plan(offsets, sorted_token, copy_pos, ranks, per_rank, capacity, status)
+    want_send, want_ret, want_overflow = ep_cpu_ops.plan(expected.padded_offsets, expected.row_token, expected.copy_row,
+                                                         ranks, per_rank, capacity)
+    assert np.array_equal(send_index.cpu().numpy(), want_send)
+    assert np.array_equal(return_row.cpu().numpy(), want_ret)
+    assert int(status.item()) == want_overflow
+
+
+def test_slot_experts_matches_the_restatement() -> None:
+    from sparsebench_b200 import _C
+
+    g = torch.Generator().manual_seed(0)
+    recv_counts = torch.randint(0, 40, (8, 16), generator=g, dtype=torch.int32)
+    recv_counts[3] = 0  # a source that sent nothing
+    for capacity in (64, 700):  # smaller and larger than what a source sent
+        got = _C.ep_slot_experts(recv_counts.cuda(), capacity)
+        assert np.array_equal(got.cpu().numpy(), ep_cpu_ops.slot_experts(recv_counts.numpy(), capacity))
+
+
+def test_gather_rows_skips_negative_indices() -> None:
+    from sparsebench_b200 import _C
+
+    src = torch.randn(50, 264, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    index = torch.tensor([3, -1, 49, 0, -1, 3], dtype=torch.int32, device="cuda")
+    out = torch.full((6, 264), 7.0, dtype=torch.bfloat16, device="cuda")
+    _C.gather_rows(src, index, out)
+    assert torch.equal(out[[0, 2, 3, 5]], src[[3, 49, 0, 3]])
+    assert torch.all(out[[1, 4]] == 7.0)
+
+
+@pytest.mark.parametrize("case", ["random", "zipf", "empty_middle"])
+def test_single_rank_step_matches_oracle_and_plain_layer(case: str) -> None:
+    from sparsebench_b200 import moe_forward
+    from sparsebench_b200.ep import ExpertParallelMoE
+
+    g = torch.Generator().manual_seed(2)
+    num_tokens, num_experts, d_model, ffn_dim = 300, 16, 256, 512
+    x = torch.randn(num_tokens, d_model, generator=g).bfloat16()
+    w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16()
+    w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16()
+    gate = torch.rand(num_tokens, 2, generator=g).bfloat16()
+    idx = routing_case(case, num_tokens, num_experts)
+    layer = ExpertParallelMoE(w1.cuda(), w2.cuda(), num_experts)
+    out = layer(x.cuda(), idx.cuda(), gate.cuda())
+    layer.check()
+    expected = M.moe_reference(x.float(), idx, gate.float(), w1.float(), w2.float())
+    torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2)
+    # Same kernels on the same rows in the same order: bit-identical to the plain layer.
+    assert torch.equal(out, moe_forward(x.cuda(), idx.cuda(), gate.cuda(), w1.cuda(), w2.cuda()))
+
+
+def test_single_rank_step_in_a_cuda_graph() -> None:
+    from sparsebench_b200.ep import ExpertParallelMoE
+    from sparsebench_b200.workloads import LayerConfig, make_layer
+
+    cfg = LayerConfig("t", 512, 256, 256, 16, "zipf")
+    layer_in = make_layer(cfg).to("cuda")
+    layer = ExpertParallelMoE(layer_in.w1, layer_in.w2, cfg.num_experts)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(layer_in.x, layer_in.expert_idx, layer_in.expert_weight)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = layer(layer_in.x, layer_in.expert_idx, layer_in.expert_weight)
+    fresh = make_layer(cfg, token_seed=9)
+    layer_in.x.copy_(fresh.x.cuda())
+    layer_in.expert_idx.copy_(fresh.expert_idx.cuda())
+    layer_in.expert_weight.copy_(fresh.expert_weight.cuda())
+    graph.replay()
+    torch.cuda.synchronize()
+    expected = M.moe_reference(fresh.x.float(), fresh.expert_idx, fresh.expert_weight.float(), fresh.w1.float(),
+                               fresh.w2.float())
+    torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2)
