@@ -107,9 +107,9 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
  * SB_ROUTE_STATIC_SCRATCH_BYTES of device memory that every GPU which loads the library holds
  * until the process exits. It calls no cudaMalloc, cudaFree or other allocating routine.
  *   - Sizes whose scratch (sb_route_workspace_bytes) exceeds the array are rejected with
- *     SB_ERR_INVALID_ARGUMENT and a message that names both numbers; 1 MiB covers e.g. 200 000
- *     copies over 1024 experts, or 8 million copies over 64 experts. Up to 32768 copies no
- *     scratch is touched at all.
+ *     SB_ERR_INVALID_ARGUMENT and a message that names both numbers; 1 MiB covers e.g. 500 000
+ *     copies over 1024 experts, or 8 million copies over 64 experts. Up to 262144 copies the
+ *     routing is a single launch and no scratch is touched at all.
  *   - The first call on a device looks the array's device address up (once per device, with that
  *     device current). Make that first call outside of any stream capture.
  *   - All calls share the one array, which simply keeps whatever the last call left in it; nothing

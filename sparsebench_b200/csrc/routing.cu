@@ -6,29 +6,38 @@
 // (csrc/routing.cu:197-281), including the -1 / flat tails of the worst-case sized buffers.
 //
 // How order is kept without atomics: a warp walks a contiguous run of copies 32 at a time, in copy
-// order. Inside one step __match_any_sync gives every lane the set of lanes holding the same
-// expert; the number of those below it is its rank, and the lowest of them alone updates that
-// warp's private per-expert counter. Runs are laid out in copy order (warp 0's run first), so an
-// exclusive scan of the counters over (chunk, warp) for each expert gives every run its base, and
-// base + running count + rank is the copy's position inside its expert. Nothing depends on which
-// thread wins a race, so two launches always agree.
+// order. Inside one step every lane learns which lanes hold the same expert (one ballot per bit of
+// the id; the same mask __match_any_sync gives, which was measured far slower here); the number of
+// those below it is its rank, and the lowest of them alone updates that warp's private per-expert
+// counter. Runs are laid out in copy order (block 0 warp 0 first), so an exclusive scan of the
+// counters over (block, warp) for each expert gives every run its base, and base + running count +
+// rank is the copy's position inside its expert. Nothing depends on which thread wins a race, so
+// two launches always agree.
 //
 // Two launch shapes:
-//   small (n <= kSingleCtaMaxCopies): ONE block of 1024 threads does count, scan, scatter and the
-//       layout arrays. This is the hot-path shape (8192 copies per layer call).
-//   large: chunk histograms -> one-block scan -> scatter + layout, three launches.
+//   cluster (n <= 262144 copies): ONE launch of a thread-block cluster (1-8 blocks of 1024 threads)
+//       does count, scan, scatter and the layout arrays; the blocks share their per-expert counts
+//       through distributed shared memory. This is the hot-path shape (8192 copies per layer call).
+//   large: chunk histograms -> one-block scan -> scatter + layout, three launches and a scratch
+//       buffer of chunks x (E + 1) ints.
 // Padding rows and rows past the real end get row_token = -1 from the layout pass itself (a row
 // is written exactly once, by the scatter or by the fill), so no memset is needed.
+
+#include <cooperative_groups.h>
 
 #include "sb_common.cuh"
 
 namespace sb {
 namespace {
 
+namespace cg = cooperative_groups;
+
 constexpr int kMaxExperts = 1024;  // one thread per expert in the scan block (reference: csrc/routing.cu:31)
 constexpr unsigned kFullMask = 0xffffffffu;
-constexpr int64_t kSingleCtaMaxCopies = 32768;
-constexpr int kSingleCtaThreads = 1024;
+constexpr int kClusterThreads = 1024;
+constexpr int kMaxClusterBlocks = 8;    // the portable cluster size limit
+constexpr int kMaxRunSteps = 32;        // 32-copy steps a warp keeps in registers
+constexpr int64_t kClusterMaxCopies = static_cast<int64_t>(kMaxClusterBlocks) * kClusterThreads * kMaxRunSteps;  // 262144
 constexpr int kChunkThreads = 256;
 constexpr int kChunkWarps = kChunkThreads / 32;
 constexpr int kChunkCopies = 2048;  // copies per block in the large shape
@@ -54,29 +63,38 @@ __device__ __forceinline__ bool load_run(const index_t* __restrict__ expert_idx,
   return bad;
 }
 
+// Lanes of the warp that hold the same expert as this lane (0 for a lane without a valid copy).
+// Same mask __match_any_sync(active, e) returns, built from one ballot per bit of the expert id:
+// on B200 the match instruction took about 65 cycles per DISTINCT value in the warp (1740 cycles
+// per step with 64 uniformly used experts), log2(E) ballots take a small constant.
+__device__ __forceinline__ unsigned same_expert_lanes(int32_t e, bool valid, int id_bits) {
+  unsigned peers = __ballot_sync(kFullMask, valid);
+  for (int b = 0; b < id_bits; ++b) {
+    const bool bit = (e >> b) & 1;
+    const unsigned with_bit = __ballot_sync(kFullMask, bit);
+    peers &= bit ? with_bit : ~with_bit;
+  }
+  return valid ? peers : 0u;
+}
+
 // One warp walks its run 32 copies per step, in copy order, and adds it to its private counters.
 // For every copy it also returns pos = the number of copies of the same expert that come earlier in
-// this run: __match_any_sync gives the lanes holding the same expert, the ones below count towards
-// pos, and the lowest of them alone reads and advances the counter (one writer per expert per step)
-// and hands the old value to its peers. Nothing here depends on timing, so the order is stable.
+// this run: the lanes holding the same expert below this one count towards pos, and the lowest of
+// them alone reads and advances the counter (one writer per expert per step) and hands the old
+// value to its peers. Nothing here depends on timing, so the order is stable.
 template <int kIters>
-__device__ __forceinline__ void rank_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int32_t* counters,
-                                         int lane, int32_t (&pos)[kIters]) {
+__device__ __forceinline__ void rank_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int id_bits,
+                                         int32_t* counters, int lane, int32_t (&pos)[kIters]) {
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
     pos[it] = 0;
     if (begin + it * 32 >= end) continue;  // uniform across the warp
     const int32_t e = ids[it];
-    const bool valid = e >= 0;
-    const unsigned active = __ballot_sync(kFullMask, valid);
-    unsigned peers = 0;
+    const unsigned peers = same_expert_lanes(e, e >= 0, id_bits);
     int32_t before = 0;
-    if (valid) {
-      peers = __match_any_sync(active, e);
-      if ((peers & ((1u << lane) - 1u)) == 0) {
-        before = counters[e];
-        counters[e] = before + __popc(peers);
-      }
+    if (peers != 0 && (peers & ((1u << lane) - 1u)) == 0) {
+      before = counters[e];
+      counters[e] = before + __popc(peers);
     }
     const int leader = peers != 0 ? __ffs(peers) - 1 : lane;
     before = __shfl_sync(kFullMask, before, leader);
@@ -185,41 +203,53 @@ __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32
 }
 
 // ---------------------------------------------------------------------------------------------
-// Small shape: everything in one block.
-// Shared memory: counters[32][E] | offsets[E+1] | counts[E] | warp_sums[32].
+// Cluster shape: ONE launch of a thread-block cluster of up to 8 blocks x 1024 threads does count,
+// scan, scatter and the layout arrays. Block b of the cluster owns the b-th contiguous slice of the
+// copies; the blocks exchange their per-expert counts through distributed shared memory (each block
+// reads the others' cta_counts[] directly), so the only global traffic is the input and the outputs,
+// and the scattered row_token stores are spread over as many SMs as the cluster has blocks.
+// Shared memory per block: counters[32][E+1] | cta_counts[E] | offsets[E+1] | counts[E] | cta_base[E]
+//                          | warp_sums[32] | bad[1].   (E+1: conflict-free column walks.)
 template <typename index_t, int kIters>
-__global__ void __launch_bounds__(kSingleCtaThreads, 1)
-route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t k, int32_t num_experts,
-                          int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
-                          int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
-                          int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
+__global__ void __launch_bounds__(kClusterThreads, 1)
+route_cluster_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t k, int32_t num_experts, int32_t id_bits,
+                     int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
+                     int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
+                     int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int cta = static_cast<int>(cluster.block_rank());
+  const int num_ctas = static_cast<int>(cluster.num_blocks());
   extern __shared__ int32_t smem[];
-  constexpr int kWarps = kSingleCtaThreads / 32;
-  int32_t* counters = smem;                                // [kWarps][E]
-  int32_t* offsets = counters + kWarps * num_experts;      // [E + 1]
-  int32_t* counts = offsets + num_experts + 1;             // [E]
-  int32_t* warp_sums = counts + num_experts;               // [32]
+  constexpr int kWarps = kClusterThreads / 32;
+  const int stride = num_experts + 1;
+  int32_t* counters = smem;                         // [kWarps][stride]
+  int32_t* cta_counts = counters + kWarps * stride; // [E]   read by the other blocks of the cluster
+  int32_t* offsets = cta_counts + num_experts;      // [E + 1]
+  int32_t* counts = offsets + num_experts + 1;      // [E]   totals over the cluster
+  int32_t* cta_base = counts + num_experts;         // [E]   copies of e in earlier blocks
+  int32_t* warp_sums = cta_base + num_experts;      // [32]
+  int32_t* cta_bad = warp_sums + 32;                // [1]   read by block 0
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
 
-  // Runs of equal length, a multiple of 32 and at most kIters * 32, in copy order.
-  const int64_t run = static_cast<int64_t>((n + kSingleCtaThreads - 1) / kSingleCtaThreads) * 32;
-  const int64_t begin = min(static_cast<int64_t>(n), warp * run);
+  // Runs of equal length over all warps of the cluster, a multiple of 32, in copy order.
+  const int64_t run = static_cast<int64_t>((n + num_ctas * kClusterThreads - 1) / (num_ctas * kClusterThreads)) * 32;
+  const int64_t begin = min(static_cast<int64_t>(n), (static_cast<int64_t>(cta) * kWarps + warp) * run);
   const int64_t end = min(static_cast<int64_t>(n), begin + run);
   int32_t ids[kIters];
   const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
-  for (int i = threadIdx.x; i < kWarps * num_experts; i += kSingleCtaThreads) counters[i] = 0;
+  for (int i = threadIdx.x; i < kWarps * stride; i += kClusterThreads) counters[i] = 0;
   __syncthreads();
   int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, counters + warp * num_experts, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, counters + warp * stride, lane, pos);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
-  if (threadIdx.x == 0) error[0] = any_bad ? 1 : 0;
+  if (threadIdx.x == 0) *cta_bad = any_bad;
 
-  // Per expert: exclusive scan of the 32 warps' counters, in place. Warp w takes experts w, w + 32,
-  // ...; lane l holds the counter of warp l, so the scan is five shuffles instead of 32 serial steps.
+  // Per expert: exclusive scan of this block's 32 warp counters, in place. Warp w takes experts
+  // w, w + 32, ...; lane l holds warp l's counter, so the scan is five shuffles.
   for (int e = warp; e < num_experts; e += kWarps) {
-    int32_t* slot = counters + lane * num_experts + e;
+    int32_t* slot = counters + lane * stride + e;
     const int32_t mine = *slot;
     int32_t inclusive = mine;
     for (int d = 1; d < 32; d <<= 1) {
@@ -227,37 +257,56 @@ route_single_block_kernel(const index_t* __restrict__ expert_idx, int32_t n, int
       if (lane >= d) inclusive += below;
     }
     *slot = inclusive - mine;
-    if (lane == 31) {
-      counts[e] = inclusive;
-      tokens_per_expert[e] = inclusive;
-    }
+    if (lane == 31) cta_counts[e] = inclusive;
   }
-  __syncthreads();
+  cluster.sync();  // every block's cta_counts and cta_bad are published
+
   const int e = threadIdx.x;
-  const int32_t total = e < num_experts ? counts[e] : 0;
+  int32_t total = 0;
+  if (e < num_experts) {
+    int32_t before = 0;
+    for (int b = 0; b < num_ctas; ++b) {
+      const int32_t c = cluster.map_shared_rank(cta_counts, b)[e];
+      if (b < cta) before += c;
+      total += c;
+    }
+    cta_base[e] = before;
+    counts[e] = total;
+  }
   const int32_t padded = e < num_experts ? (total + block_size - 1) / block_size * block_size : 0;
   int32_t all_rows = 0;
   const int32_t start = block_exclusive_scan(padded, warp_sums, &all_rows);
-  if (e < num_experts) {
-    offsets[e] = start;
-    padded_offsets[e] = start;
-  }
-  if (e == 0) {
-    offsets[num_experts] = all_rows;
-    padded_offsets[num_experts] = all_rows;
+  if (e < num_experts) offsets[e] = start;
+  if (e == 0) offsets[num_experts] = all_rows;
+  if (cta == 0) {
+    if (e < num_experts) {
+      tokens_per_expert[e] = total;
+      padded_offsets[e] = start;
+    }
+    if (e == 0) {
+      padded_offsets[num_experts] = all_rows;
+      int any = 0;
+      for (int b = 0; b < num_ctas; ++b) any |= *cluster.map_shared_rank(cta_bad, b);
+      error[0] = any ? 1 : 0;
+    }
   }
   __syncthreads();
 
-  scatter_run<kIters>(ids, pos, begin, end, k, counters + warp * num_experts, offsets, copy_row, layout.row_token,
-                      lane);
-  fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, warp, kWarps, lane);
+  // This warp's base per expert = copies in earlier blocks + in earlier warps of this block.
+  int32_t* bases = counters + warp * stride;
+  for (int i = lane; i < num_experts; i += 32) bases[i] += cta_base[i];
+  __syncwarp();
+  scatter_run<kIters>(ids, pos, begin, end, k, bases, offsets, copy_row, layout.row_token, lane);
+  fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, cta * kWarps + warp,
+              num_ctas * kWarps, lane);
+  cluster.sync();  // no block may exit while another still reads its shared memory
 }
 
 // ---------------------------------------------------------------------------------------------
 // Large shape, launch 1: per-chunk histograms. chunk_counts[chunk][e], chunk_error[chunk].
 template <typename index_t>
 __global__ void __launch_bounds__(kChunkThreads)
-route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int32_t num_experts,
+route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int32_t num_experts, int32_t id_bits,
                          int32_t* __restrict__ chunk_counts, int32_t* __restrict__ chunk_error) {
   extern __shared__ int32_t smem[];  // counters[kChunkWarps][E]
   const int lane = threadIdx.x & 31;
@@ -272,7 +321,7 @@ route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int3
   int32_t ids[kIters];
   const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
   int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, smem + warp * num_experts, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane, pos);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) chunk_error[blockIdx.x] = any_bad;
 
@@ -320,6 +369,7 @@ route_scan_kernel(int32_t* __restrict__ chunk_counts, const int32_t* __restrict_
 template <typename index_t>
 __global__ void __launch_bounds__(kChunkThreads)
 route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, int32_t k, int32_t num_experts,
+                            int32_t id_bits,
                             int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t num_chunks,
                             const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ tokens_per_expert,
                             const int32_t* __restrict__ padded_offsets, int32_t* __restrict__ copy_row,
@@ -345,7 +395,7 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
   for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
   __syncthreads();
   int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, smem + warp * num_experts, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane, pos);
   __syncthreads();
   const int32_t* base = chunk_base + static_cast<int64_t>(blockIdx.x) * num_experts;
   for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
@@ -363,12 +413,51 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
                       lane);
 }
 
-size_t single_block_smem_bytes(int32_t num_experts) {
-  return (static_cast<size_t>(kSingleCtaThreads / 32) * num_experts + 2 * static_cast<size_t>(num_experts) + 1 + 32) *
-         sizeof(int32_t);
+size_t cluster_smem_bytes(int32_t num_experts) {
+  const size_t e = static_cast<size_t>(num_experts);
+  return ((kClusterThreads / 32) * (e + 1) + e + (e + 1) + e + e + 32 + 1) * sizeof(int32_t);
 }
 
 int64_t num_chunks_for(int64_t n) { return (n + kChunkCopies - 1) / kChunkCopies; }
+
+// Bits needed to tell expert ids 0 .. num_experts-1 apart.
+int32_t id_bits_for(int32_t num_experts) {
+  int32_t bits = 0;
+  while ((1 << bits) < num_experts) ++bits;
+  return bits;
+}
+
+template <typename index_t, int kIters>
+int launch_cluster(int device, int blocks, size_t smem, cudaStream_t stream, const index_t* expert_idx, int32_t n,
+                   int32_t k, int32_t num_experts, int32_t id_bits, int32_t ffn_blocks, int32_t block_size,
+                   int32_t max_row_blocks, int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* copy_row,
+                   LayoutOut layout, int32_t* error) {
+  static bool attr_done[kMaxDevices] = {};
+  auto kernel = route_cluster_kernel<index_t, kIters>;
+  if (!attr_done[device]) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(cluster_smem_bytes(kMaxExperts)));
+    if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
+    attr_done[device] = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(blocks));
+  config.blockDim = dim3(kClusterThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(blocks);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, expert_idx, n, k, num_experts, id_bits, ffn_blocks,
+                                             block_size, max_row_blocks, tokens_per_expert, padded_offsets, copy_row,
+                                             layout, error);
+  if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing (cluster): %s", cudaGetErrorString(err));
+  return check_launch("routing (cluster)");
+}
 
 template <typename index_t>
 int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_experts, int32_t ffn_blocks,
@@ -377,30 +466,24 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   int device = 0;
   const DeviceInfo* info = current_device_info(&device);
   if (info == nullptr) return SB_ERR_CUDA;
+  const int32_t id_bits = id_bits_for(num_experts);
 
-  if (n <= kSingleCtaMaxCopies) {
-    const size_t smem = single_block_smem_bytes(num_experts);
+  if (n <= kClusterMaxCopies) {
+    // One block per 1024 copies up to the cluster limit, then longer runs per warp.
+    int blocks = static_cast<int>((n + kClusterThreads - 1) / kClusterThreads);
+    if (blocks > kMaxClusterBlocks) blocks = kMaxClusterBlocks;
+    const int64_t steps = (n + static_cast<int64_t>(blocks) * kClusterThreads - 1) / (static_cast<int64_t>(blocks) * kClusterThreads);
+    const size_t smem = cluster_smem_bytes(num_experts);
     const int32_t n32 = static_cast<int32_t>(n);
-    auto launch = [&](auto kernel, bool* attr_done) -> int {
-      if (!attr_done[device]) {
-        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     static_cast<int>(single_block_smem_bytes(kMaxExperts)));
-        if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
-        attr_done[device] = true;
-      }
-      kernel<<<1, kSingleCtaThreads, smem, stream>>>(expert_idx, n32, k, num_experts, ffn_blocks, block_size,
-                                                     max_row_blocks, tokens_per_expert, padded_offsets, copy_row,
-                                                     layout, error);
-      return SB_OK;
-    };
-    // Copies per warp = ceil(n / 1024) * 32; the kernel keeps them in kIters registers per thread.
-    static bool done8[kMaxDevices] = {}, done16[kMaxDevices] = {}, done32[kMaxDevices] = {};
-    int rc;
-    if (n <= 8 * kSingleCtaThreads) rc = launch(route_single_block_kernel<index_t, 8>, done8);
-    else if (n <= 16 * kSingleCtaThreads) rc = launch(route_single_block_kernel<index_t, 16>, done16);
-    else rc = launch(route_single_block_kernel<index_t, 32>, done32);
-    if (rc != SB_OK) return rc;
-    return check_launch("routing (single block)");
+#define SB_ROUTE_CLUSTER(ITERS)                                                                                     \
+  return launch_cluster<index_t, ITERS>(device, blocks, smem, stream, expert_idx, n32, k, num_experts, id_bits,      \
+                                        ffn_blocks, block_size, max_row_blocks, tokens_per_expert, padded_offsets,  \
+                                        copy_row, layout, error)
+    if (steps <= 1) SB_ROUTE_CLUSTER(1);
+    if (steps <= 4) SB_ROUTE_CLUSTER(4);
+    if (steps <= 16) SB_ROUTE_CLUSTER(16);
+    SB_ROUTE_CLUSTER(kMaxRunSteps);
+#undef SB_ROUTE_CLUSTER
   }
 
   const int64_t num_chunks = num_chunks_for(n);
@@ -409,7 +492,7 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   const size_t smem = static_cast<size_t>(kChunkWarps) * num_experts * sizeof(int32_t);  // <= 32 KB
 
   route_chunk_count_kernel<index_t><<<static_cast<unsigned>(num_chunks), kChunkThreads, smem, stream>>>(
-      expert_idx, n, num_experts, chunk_counts, chunk_error);
+      expert_idx, n, num_experts, id_bits, chunk_counts, chunk_error);
   if (int rc = check_launch("routing (chunk count)")) return rc;
 
   route_scan_kernel<<<1, kMaxExperts, 0, stream>>>(chunk_counts, chunk_error, static_cast<int32_t>(num_chunks),
@@ -424,8 +507,8 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   if (layout_blocks < 1) layout_blocks = 1;
   route_scatter_layout_kernel<index_t>
       <<<static_cast<unsigned>(num_chunks + layout_blocks), kChunkThreads, smem, stream>>>(
-          expert_idx, n, k, num_experts, ffn_blocks, block_size, max_row_blocks, static_cast<int32_t>(num_chunks),
-          chunk_counts, tokens_per_expert, padded_offsets, copy_row, layout);
+          expert_idx, n, k, num_experts, id_bits, ffn_blocks, block_size, max_row_blocks,
+          static_cast<int32_t>(num_chunks), chunk_counts, tokens_per_expert, padded_offsets, copy_row, layout);
   return check_launch("routing (scatter + layout)");
 }
 
@@ -484,7 +567,7 @@ int sb_route_sizes(int64_t n_copies, int32_t num_experts, int64_t ffn_dim, int64
 }
 
 size_t sb_route_workspace_bytes(int64_t n_copies, int32_t num_experts) {
-  if (n_copies <= sb::kSingleCtaMaxCopies || num_experts <= 0) return 0;
+  if (n_copies <= sb::kClusterMaxCopies || num_experts <= 0) return 0;
   const int64_t chunks = sb::num_chunks_for(n_copies);
   return static_cast<size_t>(chunks) * (static_cast<size_t>(num_experts) + 1) * sizeof(int32_t);
 }

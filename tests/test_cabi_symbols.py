@@ -64,9 +64,10 @@ def test_route_sizes_rejects_like_the_reference(lib: ctypes.CDLL, args, text: st
     assert text in lib.sb_last_error().decode()
 
 
-def test_route_workspace_is_zero_for_the_single_block_shape(lib: ctypes.CDLL) -> None:
+def test_route_workspace_is_zero_for_the_single_launch_shape(lib: ctypes.CDLL) -> None:
     assert lib.sb_route_workspace_bytes(8192, 64) == 0
-    assert lib.sb_route_workspace_bytes(200_000, 1024) == ((200_000 + 2047) // 2048) * 1025 * 4
+    assert lib.sb_route_workspace_bytes(262_144, 1024) == 0
+    assert lib.sb_route_workspace_bytes(300_000, 1024) == ((300_000 + 2047) // 2048) * 1025 * 4
 
 
 def test_null_and_shape_errors_are_reported_before_any_launch(lib: ctypes.CDLL) -> None:

@@ -51,15 +51,25 @@ def test_matches_oracle_any_k(k: int, num_tokens: int) -> None:
 @pytest.mark.parametrize("case", ["random", "skewed"])
 @pytest.mark.parametrize("num_experts", [8, 1024])
 def test_matches_oracle_big(case: str, num_experts: int) -> None:
-    # 200k copies: the three-launch shape (chunk histograms, scan, scatter + layout).
+    # 200k copies (the largest cluster shape) and 320k copies (the three-launch shape with scratch).
     check_against_oracle(routing_case(case, 100_000, num_experts), num_experts, 128)
+    check_against_oracle(routing_case(case, 160_000, num_experts), num_experts, 128)
 
 
-@pytest.mark.parametrize("num_tokens", [16383, 16384, 16385, 40000])
-def test_both_launch_shapes_around_the_switch(num_tokens: int) -> None:
-    # 32768 copies is the last size the single-block shape takes.
-    idx = routing_case("zipf", num_tokens, 128)
+@pytest.mark.parametrize("num_tokens", [511, 512, 513, 4097, 16385, 40000, 131071, 131072, 131073, 150_000])
+def test_both_launch_shapes_around_their_switches(num_tokens: int) -> None:
+    # Cluster of 1..8 blocks, 1/4/16/32 steps per warp; 262144 copies is the last size the
+    # single-launch cluster shape takes, beyond it the three-launch shape with scratch runs.
+    idx = routing_case("random", num_tokens, 128)
     check_device_buffers(idx, 128, 512, 128)
+
+
+@pytest.mark.parametrize("num_experts", [1, 2, 3, 5, 127, 129, 1000, 1024])
+def test_expert_counts_that_are_not_powers_of_two(num_experts: int) -> None:
+    # The peer mask is built from ceil(log2(E)) ballots: cover the edges of that count.
+    k = min(2, num_experts)
+    idx = random_topk(3000, num_experts, k)
+    check_device_buffers(idx, num_experts, 256, 128)
 
 
 @pytest.mark.parametrize("tag", [str(n) for n in load_golden("topology_cases.npz")["names"]])
@@ -138,10 +148,11 @@ def test_out_of_range_id_raises_without_writing_out_of_bounds() -> None:
     assert dev.copy_row.tolist() == [0, 16, 32, -1, -1, 48]  # reference: tests/test_routing.py:120
     check_device_buffers(expert_idx.cpu(), 8, 32, 16)
     # The large shape carries the flag through its scan kernel too.
-    big = routing_case("random", 30000, 64)
-    big[12345, 1] = 64
-    big[29999, 0] = -7
-    check_device_buffers(big, 64, 256, 128)
+    for num_tokens in (30000, 140000):
+        big = routing_case("random", num_tokens, 64)
+        big[12345, 1] = 64
+        big[num_tokens - 1, 0] = -7
+        check_device_buffers(big, 64, 256, 128)
 
 
 BAD_INPUTS = {

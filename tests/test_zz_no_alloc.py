@@ -48,8 +48,8 @@ def _route(lib, expert_idx: torch.Tensor, num_experts: int, ffn_dim: int, block_
     return [t.cpu().numpy() for t in outs]
 
 
-@pytest.mark.parametrize(("num_tokens", "num_experts"), [(40_000, 64), (100_000, 1024), (4096, 64)],
-                         ids=["80k-copies-E64", "200k-copies-E1024", "single-block-shape"])
+@pytest.mark.parametrize(("num_tokens", "num_experts"), [(150_000, 64), (140_000, 512), (4096, 64)],
+                         ids=["300k-copies-E64", "280k-copies-E512", "one-launch-shape"])
 def test_same_buffers_as_sb_route_two_calls_in_a_row(num_tokens: int, num_experts: int) -> None:
     lib = _lib.load()
     for call, (case, seed) in enumerate([("skewed", 1), ("random", 2)]):
