@@ -161,6 +161,9 @@ def run_reference_arm(args: argparse.Namespace) -> None:
         cfg = LayerConfig(cfg.name, cfg.num_tokens * args.gpus, cfg.d_model, cfg.ffn_dim, cfg.num_experts, cfg.routing)
     from oracle import moe as oracle_moe
 
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm is alone on the host, so it takes
+    # every core the process may run on.
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     layer = make_layer(cfg, seed=0)
     x, w = layer.x.float(), layer.expert_weight.float()
     w1, w2 = layer.w1.float(), layer.w2.float()
@@ -339,6 +342,8 @@ def main() -> None:
     parser.add_argument("--workload", default=None, choices=sorted(CONFIGS))
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--ep-capacity-factor", type=float, default=3.0,
+                        help="expert-parallel exchange rows per rank pair, as a multiple of the even share T*k/N")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -10,8 +10,9 @@ eager launches (config.launch says which).
 from __future__ import annotations
 
 import json
+import math
 import os
-import statistics
+import sys
 
 import torch
 import torch.distributed as dist
@@ -64,13 +65,23 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
     mine = range(rank * per_rank, (rank + 1) * per_rank)
     layer_in = make_layer(cfg, seed=0, token_seed=rank, experts=mine)
     dev = layer_in.to(device)
-    moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts)
+    # Rows per (source, destination) pair. T*k can never overflow but sends N times the payload; a
+    # factor over the even share T*k/N covers skewed routing (the busiest of 8 ranks draws about 2.3x
+    # its share under Zipf(1.2)). An overflow is detected on the device and fails the run below.
+    n_copies = cfg.num_tokens * cfg.k
+    factor = getattr(args, "ep_capacity_factor", 3.0)
+    capacity = min(n_copies, int(math.ceil(factor * n_copies / world / 128.0)) * 128)
+    moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=capacity)
     flush = l2_flush_buffer(device)
     hbm_gbs, bf16_tflops, peak_kind = peaks
 
     out = moe(dev.x, dev.expert_idx, dev.expert_weight)
     torch.cuda.synchronize()
-    moe.check()
+    overflow = moe.status.clone()
+    if world > 1:
+        dist.all_reduce(overflow, op=dist.ReduceOp.MAX)
+    if int(overflow.item()) != 0:
+        raise SystemExit(f"expert-parallel exchange overflowed {capacity} rows per pair: raise --ep-capacity-factor")
 
     # ---- value: graph replay if the collectives capture, else eager --------------------------------
     launch = "eager launches (graph capture of the collectives was refused)"
@@ -170,7 +181,7 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
                        "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
-                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
+                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity, "capacity_factor": factor,
                        "launch": launch, "l2": "256 MiB written before every step",
                        "frac_of_bf16_peak": value / world / bf16_tflops},
             "clocks": clocks.summary(),
@@ -181,5 +192,12 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
         }
         print(json.dumps(line))
     if world > 1:
+        # Leave without tearing the communicator down: destroying it while a captured graph still
+        # holds its collectives has been seen to block forever. Every rank has printed and
+        # synchronised by now, so a hard exit loses nothing.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)

@@ -107,8 +107,13 @@ def main() -> None:
 
     assert int(_C.device_status(torch.device("cuda", local)).item()) == 0
     print(f"rank {rank}/{world}: expert-parallel parity ok (graph replay {'ok' if graph_ok else 'not captured'})", flush=True)
+    # Hard exit after a last barrier: destroying the communicator while a captured graph still holds
+    # its collectives has been seen to block forever.
+    torch.cuda.synchronize()
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
