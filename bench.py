@@ -44,6 +44,9 @@ if str(ROOT) not in sys.path:
 from sparsebench_b200.workloads import CONFIGS, LayerConfig, make_layer  # noqa: E402
 
 METRIC = "moe_fwd_useful_tflops"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/bsr_gemm_kernel_fine_grained.md (same workload, same kernels).
+NCU_TRAFFIC_BYTES = {("fine_grained", "sdd"): 608.3e6, ("fine_grained", "dsd"): 642.2e6}
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 FALLBACK_BF16_TFLOPS = 1590.0
 
@@ -289,7 +292,7 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     roofline.update({
         "kernel": f"bsr_gemm_kernel<{dominant}>", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
         "launch_ms": stage_ms[dominant], "algorithmic_bytes": stage_bytes[dominant], "live_rows": rows,
-        "traffic": None,
+        "traffic": NCU_TRAFFIC_BYTES.get((cfg.name, dominant)),
         "stages_ms": stage_ms,
         "stages_frac_of_hbm_peak": {s: stage_bytes[s] / (stage_ms[s] * 1e-3) / 1e9 / hbm_gbs for s in stage_bytes},
         "stages_useful_tflops": {s: stage_flops[s] / (stage_ms[s] * 1e-3) / 1e12 for s in stage_flops},

@@ -137,6 +137,22 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (p.dev_status != nullptr) atomicOr(p.dev_status, bit);
   };
 
+  // What a role needs to know about a tile before it can start on it. Every role fetches the next
+  // tile's record while it works on the current one, so these dependent global loads (row_offsets,
+  // then the expert) are off the critical path at every tile boundary.
+  struct TileInfo {
+    int32_t begin, end, expert;
+  };
+  auto load_tile_info = [&](int32_t tile) {
+    const int32_t rb = tile / p.num_slices;
+    TileInfo info;
+    info.begin = __ldg(p.row_offsets + rb);
+    info.end = __ldg(p.row_offsets + rb + 1);
+    info.expert = kIsSdd ? __ldg(p.row_block_expert + rb) : 0;
+    return info;
+  };
+  const int32_t tile_step = static_cast<int32_t>(gridDim.x);
+
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -145,17 +161,24 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint64_t stream_once = ptx::policy_evict_first();
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int32_t tile = blockIdx.x;
+      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0};
+      int32_t first_col = (!kIsSdd && cur.begin != cur.end) ? __ldg(p.col_indices + cur.begin) : 0;
+      for (; ok && tile < total_tiles; tile += tile_step) {
+        const int32_t next_tile = tile + tile_step;
+        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0};
+        int32_t next_first_col = 0;
         const int32_t rb = tile / p.num_slices;
         const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
-        const int32_t begin = p.row_offsets[rb];
-        const int32_t end = p.row_offsets[rb + 1];
-        if (begin == end) continue;
-        const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2;
-        const int32_t b_row_base = kIsSdd ? p.row_block_expert[rb] * p.d_model : 0;
+        const int32_t begin = cur.begin;
+        const int32_t end = cur.end;
+        const int32_t k_steps = begin == end ? 0 : (kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2);
+        const int32_t b_row_base = kIsSdd ? cur.expert * p.d_model : 0;
         int32_t col_block = 0;
-        int32_t col_block_next = kIsSdd ? 0 : p.col_indices[begin];
+        int32_t col_block_next = first_col;
         for (int32_t ks = 0; ks < k_steps; ++ks) {
+          // A few steps in, the next tile's record has arrived: fetch its first column index too.
+          if (!kIsSdd && ks == 4 && next.begin != next.end) next_first_col = __ldg(p.col_indices + next.begin);
           if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
             give_up(SB_DEV_TIMEOUT_PRODUCER);
             ok = false;
@@ -183,6 +206,9 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ptx::tma_load_2d_hint(b_dst + j * Cfg::kBSlabBytes, &map_b, n0 + j * 64, b_row, bar, stream_once);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
+        if (!kIsSdd && k_steps <= 4 && next.begin != next.end) next_first_col = __ldg(p.col_indices + next.begin);
+        cur = next;
+        first_col = next_first_col;
       }
     }
   } else if (warp == 1) {
@@ -191,10 +217,14 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       constexpr uint32_t kIdesc = ptx::make_idesc_bf16(Cfg::kTileM, kTileN, /*b_mn_major=*/true);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int32_t rb = tile / p.num_slices;
-        const int32_t begin = p.row_offsets[rb];
-        const int32_t end = p.row_offsets[rb + 1];
+      int32_t tile = blockIdx.x;
+      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0};
+      for (; ok && tile < total_tiles; tile += tile_step) {
+        const int32_t next_tile = tile + tile_step;
+        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0};
+        const int32_t begin = cur.begin;
+        const int32_t end = cur.end;
+        cur = next;
         if (begin == end) continue;
         const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2;
         if (!ptx::mbar_wait_bounded(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_word)) {
@@ -313,14 +343,23 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     bool ok = true;
     int32_t tile = blockIdx.x;
     int32_t tok[8];
-    if (tile < total_tiles) load_tokens(tile, tok);
+    TileInfo cur = TileInfo{0, 0, 0};
+    if (tile < total_tiles) {
+      load_tokens(tile, tok);
+      cur = load_tile_info(tile);
+    }
     while (ok && tile < total_tiles) {
-      // The next tile's row -> token table is fetched while this tile is gathered.
-      const int32_t next = tile + static_cast<int32_t>(gridDim.x);
+      // The next tile's record and row -> token table are fetched while this tile is gathered.
+      const int32_t next = tile + tile_step;
       int32_t tok_next[8];
-      if (next < total_tiles) load_tokens(next, tok_next);
-      const int32_t rb = tile / p.num_slices;
-      if (p.row_offsets[rb] != p.row_offsets[rb + 1]) {
+      TileInfo next_info = TileInfo{0, 0, 0};
+      if (next < total_tiles) {
+        load_tokens(next, tok_next);
+        next_info = load_tile_info(next);
+      }
+      const bool live = cur.begin != cur.end;
+      cur = next_info;
+      if (live) {
         const __nv_bfloat16* src[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
