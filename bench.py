@@ -347,6 +347,8 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--ep-capacity-factor", type=float, default=3.0,
                         help="expert-parallel exchange rows per rank pair, as a multiple of the even share T*k/N")
+    parser.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                        help="expert-parallel exchange: rows stored into peer memory by our kernels, or NCCL all-to-all")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -161,6 +161,28 @@ int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gat
                int64_t num_tokens, int32_t k, int32_t d_model, sb_stream_t stream);
 
 /*
+ * The layer on a flat assignment list: copy c sends token token_of_copy[c] to expert
+ * expert_of_copy[c] with weight weight_of_copy[c]; a token may have any number of copies,
+ * including none. Replaces the PyTorch steps of sparsebench::moe_forward_assigned
+ * (sparsebench/moe.py:59-91). The copies go through sb_route as a k = 1 problem, then:
+ *
+ * sb_remap_rows: row_token[r] = row_copy[r] >= 0 ? token_of_copy[row_copy[r]] : -1, turning the
+ * copy indices k = 1 routing leaves in row_token into token indices (moe.py:78-81). May run in
+ * place (row_token == row_copy). token_of_copy is int32 or int64.
+ *
+ * sb_combine_assigned: out[t][:] = bf16( sum over copies c of token t of
+ * float(y[copy_row[c]][:]) * float(weight[c]) ), zero for a token without copies (moe.py:87-91).
+ * accumulator is caller-provided fp32 scratch [num_tokens * d_model] (cleared here); the sum uses
+ * atomic adds like the reference's index_add_, so its last bits can depend on the order.
+ * weight_dtype: 0 = bf16, 1 = fp32. d_model % 4 == 0.
+ */
+int sb_remap_rows(const int32_t* row_copy, const void* token_of_copy, int token_is_i64, int32_t* row_token,
+                  int64_t num_rows, int64_t num_copies, sb_stream_t stream);
+int sb_combine_assigned(const void* y, const int32_t* copy_row, const void* token_of_copy, int token_is_i64,
+                        const void* weight, int weight_dtype, float* accumulator, void* out, int64_t num_copies,
+                        int64_t num_tokens, int32_t d_model, sb_stream_t stream);
+
+/*
  * ---- Expert-parallel plumbing (no counterpart in the reference, which is single-GPU) ----------
  *
  * N ranks, E experts in total, rank d owns experts [d*experts_per_rank, (d+1)*experts_per_rank).
@@ -170,7 +192,11 @@ int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gat
  * fixed capacity of `capacity` rows per (source, destination) pair, so no size depends on a count
  * the host does not know. The exchanges themselves are all-to-alls of the caller's choosing (NCCL).
  */
-enum sb_ep_status { SB_EP_OK = 0, SB_EP_OVERFLOW = 1 /* a pair's run exceeded `capacity`: copies dropped */ };
+enum sb_ep_status {
+  SB_EP_OK = 0,
+  SB_EP_OVERFLOW = 1, /* a pair's run exceeded `capacity`: copies dropped */
+  SB_EP_TIMEOUT = 2   /* sb_ep_barrier gave up waiting for a peer */
+};
 
 /*
  * send_index[d*capacity + i] = source token of the i-th copy bound for rank d, -1 past the run;
@@ -198,6 +224,30 @@ int sb_ep_slot_experts(const int32_t* recv_counts, int32_t num_ranks, int32_t ex
  */
 int sb_gather_rows(const void* src, const int32_t* index, void* out, int64_t num_out_rows, int32_t row_bytes,
                    sb_stream_t stream);
+
+/*
+ * Exchange over peer memory (NVLink / NVSwitch) instead of a collective library: every rank maps
+ * the others' exchange buffers (e.g. CUDA VMM / symmetric memory; mapping them is the caller's job)
+ * and passes device arrays of the N base pointers.
+ *
+ * sb_ep_push_rows: for every slot j = peer*capacity + i with index[j] >= 0, stores row
+ * src[index[j]] into peer_base[peer] at row my_rank*capacity + i. Only real rows cross the link, so
+ * the traffic is the payload, whatever the capacity. Dispatch: src = x, index = send_index; return:
+ * src = y, index = the owner's copy_row over its receive slots.
+ * sb_ep_push_counts: counts[d*experts_per_rank + e] -> peer_counts[d][my_rank*experts_per_rank + e].
+ * sb_ep_barrier: all ranks wait for each other on the device. peer_pads[p] is rank p's pad of
+ * num_ranks words (zeroed once before the first call), my_pad this rank's own, epoch_word a local
+ * device counter the kernel advances (so a captured graph stays valid across replays). Stores
+ * issued before the barrier, remote ones included, are visible to every rank after it. The wait
+ * is bounded (2 s): on expiry SB_EP_TIMEOUT is OR-ed into *status and the kernel returns.
+ * Every rank must call it the same number of times.
+ */
+int sb_ep_push_rows(const void* src, const int32_t* index, void* const* peer_base, int32_t my_rank,
+                    int32_t num_ranks, int32_t capacity, int32_t row_bytes, sb_stream_t stream);
+int sb_ep_push_counts(const int32_t* counts, int32_t* const* peer_counts, int32_t my_rank, int32_t num_ranks,
+                      int32_t experts_per_rank, sb_stream_t stream);
+int sb_ep_barrier(uint32_t* const* peer_pads, uint32_t* my_pad, uint32_t* epoch_word, int32_t my_rank,
+                  int32_t num_ranks, int32_t* status, sb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -127,3 +127,16 @@ def moe_reference_streamed(x, expert_idx, expert_weight, w1, w2, dtype=torch.flo
         y = F.gelu(xf[token] @ w1[e].to(dtype)) @ w2[e].to(dtype)
         out.index_add_(0, token, y * wf[token, slot, None])
     return out
+
+
+def moe_assigned_reference(x, token_of_copy, expert_of_copy, weight_of_copy, w1, w2) -> torch.Tensor:
+    """The layer on a flat assignment list, expert by expert: copy c sends token token_of_copy[c] to
+    expert expert_of_copy[c] with weight weight_of_copy[c]; tokens without copies stay 0 (the check
+    the reference's tests use for moe_forward_assigned: tests/test_token_rounding.py:90-97)."""
+    out = torch.zeros(x.shape[0], x.shape[1], dtype=x.dtype)
+    for e in range(w1.shape[0]):
+        mask = expert_of_copy == e
+        if mask.any():
+            y = F.gelu(x[token_of_copy[mask]] @ w1[e]) @ w2[e]
+            out.index_add_(0, token_of_copy[mask], y * weight_of_copy[mask, None].to(x.dtype))
+    return out

@@ -188,6 +188,47 @@ def combine_cuda(y: torch.Tensor, copy_row: torch.Tensor, expert_weight: torch.T
     return out
 
 
+# ---- the layer on a flat assignment list (PyTorch ops in the reference, sparsebench/moe.py:59-91) ---
+
+def remap_rows_cuda(row_copy: torch.Tensor, token_of_copy: torch.Tensor) -> torch.Tensor:
+    """row_token[r] = token_of_copy[row_copy[r]] where row_copy[r] >= 0, else -1."""
+    lib = _lib.load()
+    _check_index(row_copy, "row_copy")
+    _check(token_of_copy.is_cuda and token_of_copy.dim() == 1 and token_of_copy.is_contiguous() and
+           token_of_copy.dtype in (torch.int32, torch.int64), "token_of_copy must be a contiguous 1-D int32/int64 CUDA tensor")
+    with torch.cuda.device(row_copy.device):
+        out = torch.empty_like(row_copy)
+        if row_copy.numel() > 0:
+            _lib.check(lib.sb_remap_rows(_ptr(row_copy), _ptr(token_of_copy), int(token_of_copy.dtype == torch.int64),
+                                         _ptr(out), row_copy.numel(), token_of_copy.numel(), _stream()))
+    return out
+
+
+def combine_assigned_cuda(y: torch.Tensor, copy_row: torch.Tensor, token_of_copy: torch.Tensor,
+                          weight_of_copy: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    """out[t] = bf16(sum over the copies c of token t of float(y[copy_row[c]]) * float(weight_of_copy[c]))."""
+    lib = _lib.load()
+    _check(y.is_cuda and y.dtype == torch.bfloat16 and y.dim() == 2 and y.is_contiguous(),
+           "y must be a contiguous [P, D] bfloat16 CUDA tensor")
+    _check_index(copy_row, "copy_row")
+    n = copy_row.numel()
+    _check(token_of_copy.numel() == n and weight_of_copy.numel() == n, "token_of_copy and weight_of_copy need one entry per copy")
+    _check(token_of_copy.dtype in (torch.int32, torch.int64) and token_of_copy.is_contiguous(),
+           "token_of_copy must be contiguous int32/int64")
+    if weight_of_copy.dtype not in (torch.bfloat16, torch.float32):
+        weight_of_copy = weight_of_copy.float()
+    weight_of_copy = weight_of_copy.contiguous()
+    _check(y.shape[1] % 4 == 0, f"D ({y.shape[1]}) must be a multiple of 4")
+    with torch.cuda.device(y.device):
+        acc = torch.empty((num_tokens, y.shape[1]), dtype=torch.float32, device=y.device)
+        out = torch.empty((num_tokens, y.shape[1]), dtype=torch.bfloat16, device=y.device)
+        _lib.check(lib.sb_combine_assigned(_ptr(y), _ptr(copy_row), _ptr(token_of_copy),
+                                           int(token_of_copy.dtype == torch.int64), _ptr(weight_of_copy),
+                                           int(weight_of_copy.dtype == torch.float32), _ptr(acc), _ptr(out), n,
+                                           num_tokens, y.shape[1], _stream()))
+    return out
+
+
 # ---- expert-parallel plumbing (no counterpart in the reference's extension) ----------------------
 
 def sort_copies_cuda(expert_idx: torch.Tensor, num_experts: int) -> list[torch.Tensor]:
@@ -258,3 +299,38 @@ def gather_rows(src: torch.Tensor, index: torch.Tensor, out: torch.Tensor | None
         if index.numel() > 0:
             _lib.check(lib.sb_gather_rows(_ptr(src), _ptr(index), _ptr(out), index.numel(), row_bytes, _stream()))
     return out
+
+
+def ep_push_rows(src: torch.Tensor, index: torch.Tensor, peer_base: torch.Tensor, my_rank: int, capacity: int) -> None:
+    """Row src[index[j]] of every slot j = peer*capacity + i with index[j] >= 0 is stored into rank
+    `peer`'s buffer (peer_base[peer], an int64 device array of mapped base addresses) at row
+    my_rank*capacity + i."""
+    lib = _lib.load()
+    _check(src.is_cuda and src.dim() == 2 and src.is_contiguous(), "src must be a contiguous 2-D CUDA tensor")
+    _check_index(index, "index")
+    _check(peer_base.is_cuda and peer_base.dtype == torch.int64 and peer_base.is_contiguous(),
+           "peer_base must be a contiguous int64 CUDA tensor of base addresses")
+    num_ranks = peer_base.numel()
+    _check(index.numel() == num_ranks * capacity, "index must have ranks * capacity entries")
+    with torch.cuda.device(src.device):
+        _lib.check(lib.sb_ep_push_rows(_ptr(src), _ptr(index), _ptr(peer_base), my_rank, num_ranks, capacity,
+                                       src.shape[1] * src.element_size(), _stream()))
+
+
+def ep_push_counts(counts: torch.Tensor, peer_counts: torch.Tensor, my_rank: int, experts_per_rank: int) -> None:
+    """counts[d*E_local + e] -> rank d's table (peer_counts[d]) at [my_rank*E_local + e]."""
+    lib = _lib.load()
+    _check_index(counts, "counts")
+    num_ranks = peer_counts.numel()
+    _check(counts.numel() == num_ranks * experts_per_rank, "counts must have ranks * experts_per_rank entries")
+    with torch.cuda.device(counts.device):
+        _lib.check(lib.sb_ep_push_counts(_ptr(counts), _ptr(peer_counts), my_rank, num_ranks, experts_per_rank, _stream()))
+
+
+def ep_barrier(peer_pads: torch.Tensor, my_pad: torch.Tensor, epoch: torch.Tensor, my_rank: int,
+               status: torch.Tensor) -> None:
+    """Device-side barrier of all ranks over peer memory (bounded wait; see sb_ep_barrier)."""
+    lib = _lib.load()
+    with torch.cuda.device(my_pad.device):
+        _lib.check(lib.sb_ep_barrier(_ptr(peer_pads), _ptr(my_pad), _ptr(epoch), my_rank, peer_pads.numel(),
+                                     _ptr(status), _stream()))

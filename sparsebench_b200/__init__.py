@@ -6,7 +6,7 @@ package does not load the CUDA library; the first operator call does, and fails 
 missing. There is no CPU or PyTorch fallback.
 """
 
-from sparsebench_b200.moe import moe_forward
+from sparsebench_b200.moe import moe_forward, moe_forward_assigned
 from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route_device
 from sparsebench_b200.spmm import combine, dsd, sdd
 from sparsebench_b200.topology import Topology
@@ -18,6 +18,7 @@ __all__ = [
     "combine",
     "dsd",
     "moe_forward",
+    "moe_forward_assigned",
     "route_device",
     "sdd",
 ]

@@ -111,6 +111,73 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ in
   }
 }
 
+// One warp per slot; lanes copy 16-byte vectors into ANOTHER rank's memory (plain stores through
+// the peer mapping, i.e. over NVLink). Slot j = (peer, i) with peer = j / capacity: the row lands in
+// the peer's buffer at [my_rank][i]. Only real rows travel; empty slots cost one index read.
+__global__ void __launch_bounds__(kThreads)
+push_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ index, uint4* const* __restrict__ peer_base,
+                 int32_t my_rank, int32_t capacity, int64_t num_slots, int32_t vecs_per_row) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); j < num_slots;
+       j += warps) {
+    const int32_t row = __ldg(index + j);
+    if (row < 0) continue;
+    const int32_t peer = static_cast<int32_t>(j / capacity);
+    const int64_t i = j - static_cast<int64_t>(peer) * capacity;
+    const uint4* s = src + static_cast<int64_t>(row) * vecs_per_row;
+    uint4* d = peer_base[peer] + (static_cast<int64_t>(my_rank) * capacity + i) * vecs_per_row;
+    for (int32_t v = lane; v < vecs_per_row; v += 32) d[v] = __ldg(s + v);
+  }
+}
+
+// counts[d*Epr + e] -> peer d's table at [my_rank*Epr + e].
+__global__ void push_counts_kernel(const int32_t* __restrict__ counts, int32_t* const* __restrict__ peer_counts,
+                                   int32_t my_rank, int32_t num_ranks, int32_t experts_per_rank) {
+  const int32_t total = num_ranks * experts_per_rank;
+  for (int32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int32_t d = i / experts_per_rank;
+    peer_counts[d][my_rank * experts_per_rank + (i - d * experts_per_rank)] = counts[i];
+  }
+}
+
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// All-ranks barrier over peer memory. One block, thread p talks to rank p: it publishes this rank's
+// new epoch in p's pad (release, system scope: everything this GPU wrote before the kernel, remote
+// stores included, is visible to whoever sees the epoch) and waits until p's epoch shows up in this
+// rank's own pad. The wait is bounded; on expiry it sets SB_EP_TIMEOUT in *status and goes on.
+constexpr uint64_t kBarrierLimitNs = 2000ull * 1000ull * 1000ull;
+__global__ void ep_barrier_kernel(uint32_t* const* __restrict__ peer_pads, uint32_t* __restrict__ my_pad,
+                                  uint32_t* __restrict__ epoch_word, int32_t my_rank, int32_t num_ranks,
+                                  int32_t* __restrict__ status) {
+  const int p = threadIdx.x;
+  const uint32_t epoch = *epoch_word + 1u;
+  __threadfence_system();
+  if (p < num_ranks) {
+    uint32_t* remote = peer_pads[p] + my_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const uint32_t* mine = my_pad + p;
+    const uint64_t start = now_ns();
+    uint32_t poll = 0;
+    while (true) {
+      uint32_t seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(seen - epoch) >= 0) break;
+      if ((++poll & 255u) == 0u && now_ns() - start > kBarrierLimitNs) {
+        atomicOr(status, SB_EP_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (p == 0) *epoch_word = epoch;
+}
+
 int64_t capped_blocks(int64_t items, int per_block, const DeviceInfo* info) {
   int64_t blocks = (items + per_block - 1) / per_block;
   const int64_t cap = static_cast<int64_t>(info->sm_count) * 16;
@@ -169,6 +236,48 @@ int sb_gather_rows(const void* src, const int32_t* index, void* out, int64_t num
                        as_stream(stream)>>>(static_cast<const uint4*>(src), index, static_cast<uint4*>(out),
                                             num_out_rows, row_bytes / 16);
   return check_launch("gather_rows");
+}
+
+int sb_ep_push_rows(const void* src, const int32_t* index, void* const* peer_base, int32_t my_rank,
+                    int32_t num_ranks, int32_t capacity, int32_t row_bytes, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!src || !index || !peer_base) return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_rows: NULL buffer");
+  if (num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || capacity <= 0 || row_bytes <= 0 || row_bytes % 16 != 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_rows: need 0 <= rank < ranks, capacity > 0, row bytes a multiple of 16");
+  if (!aligned16(src)) return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_rows: src must be 16-byte aligned");
+  const DeviceInfo* info = current_device_info();
+  if (info == nullptr) return SB_ERR_CUDA;
+  const int64_t slots = static_cast<int64_t>(num_ranks) * capacity;
+  push_rows_kernel<<<static_cast<unsigned>(capped_blocks(slots, kThreads / 32, info)), kThreads, 0, as_stream(stream)>>>(
+      static_cast<const uint4*>(src), index, reinterpret_cast<uint4* const*>(peer_base), my_rank, capacity, slots,
+      row_bytes / 16);
+  return check_launch("ep_push_rows");
+}
+
+int sb_ep_push_counts(const int32_t* counts, int32_t* const* peer_counts, int32_t my_rank, int32_t num_ranks,
+                      int32_t experts_per_rank, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!counts || !peer_counts) return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_counts: NULL buffer");
+  if (num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || experts_per_rank <= 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_counts: bad rank or size");
+  const int total = num_ranks * experts_per_rank;
+  push_counts_kernel<<<(total + kThreads - 1) / kThreads, kThreads, 0, as_stream(stream)>>>(counts, peer_counts, my_rank,
+                                                                                         num_ranks, experts_per_rank);
+  return check_launch("ep_push_counts");
+}
+
+int sb_ep_barrier(uint32_t* const* peer_pads, uint32_t* my_pad, uint32_t* epoch_word, int32_t my_rank,
+                  int32_t num_ranks, int32_t* status, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!peer_pads || !my_pad || !epoch_word || !status) return fail(SB_ERR_INVALID_ARGUMENT, "ep_barrier: NULL buffer");
+  if (num_ranks <= 0 || num_ranks > 1024 || my_rank < 0 || my_rank >= num_ranks)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_barrier: need 0 <= rank < ranks <= 1024");
+  const int threads = (num_ranks + 31) / 32 * 32;
+  ep_barrier_kernel<<<1, threads, 0, as_stream(stream)>>>(peer_pads, my_pad, epoch_word, my_rank, num_ranks, status);
+  return check_launch("ep_barrier");
 }
 
 }  // extern "C"

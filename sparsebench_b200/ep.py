@@ -84,6 +84,67 @@ class CudaOps:
 
         return _C.combine_cuda(y, copy_row, expert_weight)
 
+    def push_rows(self, src, index, peer_base, my_rank, capacity) -> None:
+        from sparsebench_b200 import _C
+
+        _C.ep_push_rows(src, index, peer_base, my_rank, capacity)
+
+    def push_counts(self, counts, peer_counts, my_rank, experts_per_rank) -> None:
+        from sparsebench_b200 import _C
+
+        _C.ep_push_counts(counts, peer_counts, my_rank, experts_per_rank)
+
+    def barrier(self, peer_pads, my_pad, epoch, my_rank, status) -> None:
+        from sparsebench_b200 import _C
+
+        _C.ep_barrier(peer_pads, my_pad, epoch, my_rank, status)
+
+
+class PeerExchange:
+    """Exchange buffers of one rank mapped into every other rank (torch symmetric memory: CUDA VMM
+    handles exchanged once at set-up), so that rows are stored straight into their owner's memory
+    over NVLink and only real rows travel. Holds, per rank: recv [N*C, D] (dispatched rows, block s
+    from rank s), ret [N*C, D] (results coming back, block d from rank d), counts [N, E/N] and a pad
+    of N words for the device-side barrier."""
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, capacity: int, d_model: int,
+                 experts_local: int, dtype: torch.dtype = torch.bfloat16) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        world = self.world
+        elem = torch.empty(0, dtype=dtype).element_size()
+
+        def aligned(n: int) -> int:
+            return (n + 255) // 256 * 256
+
+        rows_bytes = aligned(world * capacity * d_model * elem)
+        counts_bytes = aligned(world * experts_local * 4)
+        pad_bytes = aligned(world * 4)
+        offsets = [0, rows_bytes, 2 * rows_bytes, 2 * rows_bytes + counts_bytes]
+        total = offsets[3] + pad_bytes
+        self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buffer, group)
+        self.buffer[offsets[2]:].zero_()  # counts and barrier pad start at zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+        def view(off: int, nbytes: int, dt: torch.dtype) -> torch.Tensor:
+            return self.buffer[off : off + nbytes].view(dt)
+
+        self.recv = view(offsets[0], world * capacity * d_model * elem, dtype).view(world * capacity, d_model)
+        self.ret = view(offsets[1], world * capacity * d_model * elem, dtype).view(world * capacity, d_model)
+        self.counts = view(offsets[2], world * experts_local * 4, torch.int32).view(world, experts_local)
+        self.pad = view(offsets[3], world * 4, torch.int32)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+
+        def table(off: int) -> torch.Tensor:
+            return torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
+
+        self.peer_recv, self.peer_ret = table(offsets[0]), table(offsets[1])
+        self.peer_counts, self.peer_pads = table(offsets[2]), table(offsets[3])
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+
 
 @dataclass
 class StepTrace:
@@ -101,9 +162,13 @@ class ExpertParallelMoE:
     """One rank's share of an expert-parallel layer."""
 
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
-                 group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None) -> None:
+                 group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
+                 exchange: str = "nccl") -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
-        (source, destination) pair; None means T*k of the first call's batch (never overflows)."""
+        (source, destination) pair; None means T*k of the first call's batch (never overflows).
+        `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
+        "peer" = rows stored straight into the owner's mapped memory by this library's kernels, with a
+        device-side barrier (only real rows travel; needs `capacity` up front and world size > 1)."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -116,8 +181,16 @@ class ExpertParallelMoE:
         self.num_experts, self.experts_local, self.d_model, self.ffn_dim = num_experts, experts_local, d_model, ffn_dim
         self.capacity = capacity
         self.ops = ops if ops is not None else CudaOps()
-        self.status = torch.zeros(1, dtype=torch.int32, device=w1_local.device)  # SB_EP_OVERFLOW bits
+        self.status = torch.zeros(1, dtype=torch.int32, device=w1_local.device)  # sb_ep_status bits
         self.last: StepTrace | None = None
+        if exchange not in ("nccl", "peer"):
+            raise ValueError(f"exchange must be 'nccl' or 'peer', got {exchange!r}")
+        self.peer: PeerExchange | None = None
+        if exchange == "peer" and self.world > 1:
+            if capacity is None:
+                raise ValueError("the peer exchange sizes its buffers at construction: pass `capacity`")
+            self.peer = PeerExchange(group if group is not None else dist.group.WORLD, w1_local.device, capacity,
+                                     d_model, experts_local, w1_local.dtype)
 
     def _all_to_all(self, send: torch.Tensor) -> torch.Tensor:
         """[N, ...] -> [N, ...]: block d goes to rank d, block s of the result came from rank s."""
@@ -128,8 +201,12 @@ class ExpertParallelMoE:
         return recv
 
     def check(self) -> None:
-        """Syncs. Raises if some (source, destination) run exceeded the capacity and copies were dropped."""
-        if int(self.status.item()) != 0:
+        """Syncs. Raises if some (source, destination) run exceeded the capacity and copies were
+        dropped, or if a device-side barrier gave up waiting for a peer."""
+        status = int(self.status.item())
+        if status & 2:
+            raise RuntimeError("expert-parallel barrier timed out waiting for a peer rank")
+        if status & 1:
             raise RuntimeError("expert-parallel exchange overflowed its capacity: raise `capacity`")
 
     def forward(self, x: torch.Tensor, expert_idx: torch.Tensor, expert_weight: torch.Tensor,
@@ -148,6 +225,9 @@ class ExpertParallelMoE:
         send_index, return_row = ops.plan(offsets, sorted_token, copy_pos, world, self.experts_local, capacity,
                                           self.status)
         mark("dispatch plan")
+        if self.peer is not None:
+            return self._forward_peer(x, expert_weight, counts, send_index, return_row, mark,
+                                      (counts, offsets, sorted_token, copy_pos))
         # 3. Pack and exchange rows and counts.
         send = ops.gather_rows(x, send_index)  # [N*C, D]; rows of empty slots are never read
         recv_counts = self._all_to_all(counts.view(world, self.experts_local))
@@ -168,6 +248,28 @@ class ExpertParallelMoE:
         out = ops.combine(returned, return_row, expert_weight)
         mark("combine")
         self.last = StepTrace((counts, offsets, sorted_token, copy_pos), send_index, return_row, recv_counts, slot_expert, topo)
+        return out
+
+    def _forward_peer(self, x, expert_weight, counts, send_index, return_row, mark, source_sort) -> torch.Tensor:
+        """Steps 3-5 with the rows stored directly into their owners' memory."""
+        ops, peer, capacity = self.ops, self.peer, self.capacity
+        ops.push_counts(counts, peer.peer_counts, self.rank, self.experts_local)
+        ops.push_rows(x, send_index, peer.peer_recv, self.rank, capacity)
+        ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)
+        mark("dispatch all-to-all")
+        slot_expert = ops.slot_experts(peer.counts, capacity)
+        topo = ops.route(slot_expert.view(-1, 1), self.experts_local, self.ffn_dim, BLOCK_SIZE)
+        mark("routing")
+        h = ops.sdd(peer.recv, self.w1, topo)
+        mark("SDD + GELU (fused)")
+        y = ops.dsd(h, self.w2_cat, topo)
+        mark("DSD")
+        ops.push_rows(y, topo.copy_row, peer.peer_ret, self.rank, capacity)
+        ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)
+        mark("return all-to-all")
+        out = ops.combine(peer.ret, return_row, expert_weight)
+        mark("combine")
+        self.last = StepTrace(source_sort, send_index, return_row, peer.counts, slot_expert, topo)
         return out
 
     __call__ = forward

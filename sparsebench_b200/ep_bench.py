@@ -71,7 +71,24 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
     n_copies = cfg.num_tokens * cfg.k
     factor = getattr(args, "ep_capacity_factor", 3.0)
     capacity = min(n_copies, int(math.ceil(factor * n_copies / world / 128.0)) * 128)
-    moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=capacity)
+    exchange = getattr(args, "ep_exchange", "peer") if world > 1 else "nccl"
+    moe = None
+    if exchange == "peer":
+        # Rows stored straight into the owner's memory: only real rows travel, so the capacity can be
+        # the exact worst case. If the buffers cannot be mapped on this machine every rank falls back.
+        try:
+            moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer")
+            mapped = torch.ones(1, device=device)
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+            mapped = torch.zeros(1, device=device)
+            peer_error = repr(exc)
+        dist.all_reduce(mapped, op=dist.ReduceOp.MIN)
+        if mapped.item() == 0:
+            moe, exchange = None, "nccl (peer mapping failed: %s)" % locals().get("peer_error", "on another rank")
+        else:
+            capacity = n_copies
+    if moe is None:
+        moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=capacity)
     flush = l2_flush_buffer(device)
     hbm_gbs, bf16_tflops, peak_kind = peaks
 
@@ -170,7 +187,7 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
         "kernel": f"bsr_gemm_kernel<{dominant}> on rank 0", "peak_source": peak_kind, "launch_ms": gemm_ms[dominant],
         "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "traffic": None, "stages_ms": stage_ms,
         "all_to_all": {"useful_bytes_per_direction": payload,
-                       "sent_bytes_per_direction": world * moe.capacity * cfg.d_model * 2,
+                       "sent_bytes_per_direction": payload if moe.peer is not None else world * moe.capacity * cfg.d_model * 2,
                        "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},
     })
 
@@ -181,7 +198,7 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
                        "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
-                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity, "capacity_factor": factor,
+                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity, "exchange": exchange,
                        "launch": launch, "l2": "256 MiB written before every step",
                        "frac_of_bf16_peak": value / world / bf16_tflops},
             "clocks": clocks.summary(),

@@ -9,10 +9,12 @@ with new tokens and new routing.
 
 from __future__ import annotations
 
+import dataclasses
 from collections.abc import Callable
 
 import torch
 
+from sparsebench_b200 import _C
 from sparsebench_b200.routing import route_device
 from sparsebench_b200.spmm import combine, dsd, sdd
 
@@ -53,3 +55,33 @@ def moe_forward(
     out = combine(y, expert_weight, topo)
     mark("combine")
     return out
+
+
+def moe_forward_assigned(
+    x: torch.Tensor,
+    token_of_copy: torch.Tensor,
+    expert_of_copy: torch.Tensor,
+    weight_of_copy: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+) -> torch.Tensor:
+    """The same layer for any routing given as a flat list: copy c sends token token_of_copy[c] to
+    expert expert_of_copy[c] with weight weight_of_copy[c]. A token may have any number of copies,
+    including none (its output row is 0), e.g. after a router that rounds per-expert counts
+    (reference: sparsebench/moe.py:59-91).
+
+    The copies go through routing as a k = 1 problem; the row -> copy table it leaves is turned into
+    row -> token by one small kernel, SDD and DSD run unchanged, and the combine adds each copy's
+    weighted row into its token in fp32. Still no host sync."""
+    num_experts, d_model, ffn_dim = w1.shape
+    num_tokens = x.shape[0]
+    if expert_of_copy.numel() == 0:  # host-known size: nothing routed anywhere
+        return torch.zeros_like(x)
+
+    topo = route_device(expert_of_copy.reshape(-1, 1).contiguous(), num_experts, ffn_dim, BLOCK_SIZE)
+    token_of_copy = token_of_copy.contiguous()
+    # With k = 1 routing's row_token holds copy indices (-1 for padding): map them to tokens.
+    topo = dataclasses.replace(topo, row_token=_C.remap_rows_cuda(topo.row_token, token_of_copy))
+    h = sdd(x, w1, topo, gelu=True)
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5)
+    return _C.combine_assigned_cuda(y, topo.copy_row, token_of_copy, weight_of_copy, num_tokens)
