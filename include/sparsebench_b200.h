@@ -142,8 +142,8 @@ int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_
  * DSD: y[rb*bs + r][:] = sum over p in [row_offsets[rb], row_offsets[rb+1]) of
  * h_blocks[p][r][:] . w[col_indices[p]*bs .. +bs][:], a general BSR x dense product.
  * Replaces sparsebench::dsd_cuda (csrc/dsd.cpp:27-80) and its version-5 kernel
- * (csrc/dsd_v5.cu:42-123). bf16 in/out, fp32 accumulation. block_size must be 128 and
- * d_model % 128 == 0 (the reference's block size 64 is not built: SB_ERR_UNSUPPORTED).
+ * (csrc/dsd_v5.cu:42-123). bf16 in/out, fp32 accumulation. block_size is 128 or 64 (a 64-row
+ * block uses the lower half of the 128-row tensor-core tile) and d_model % 128 == 0.
  * Rows of row blocks without blocks are left unwritten, or zeroed when zero_dead_rows != 0
  * (what the reference's versions 1-3 do).
  */

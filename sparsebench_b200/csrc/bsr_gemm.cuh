@@ -51,6 +51,7 @@ struct GemmParams {
   const int32_t* col_indices;       // [nnz]
   __nv_bfloat16* y;                 // [num_row_blocks * 128, D]
   int32_t zero_dead_rows;
+  int32_t block_rows;               // BSR block size: 128, or 64 (the tile's upper 64 rows then idle)
   // both
   int32_t d_model;
 };
@@ -152,6 +153,10 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     return info;
   };
   const int32_t tile_step = static_cast<int32_t>(gridDim.x);
+  // DSD: K steps of 64 per BSR block (block size 128 -> 2, 64 -> 1), as a shift and a mask.
+  const int32_t steps_shift = (!kIsSdd && p.block_rows == 64) ? 0 : 1;
+  const int32_t steps_mask = (1 << steps_shift) - 1;
+  const int32_t out_rows = kIsSdd ? Cfg::kTileM : p.block_rows;  // rows of the tile that are stored
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -172,7 +177,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
         const int32_t begin = cur.begin;
         const int32_t end = cur.end;
-        const int32_t k_steps = begin == end ? 0 : (kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2);
+        const int32_t k_steps = begin == end ? 0 : (kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) << steps_shift);
         const int32_t b_row_base = kIsSdd ? cur.expert * p.d_model : 0;
         int32_t col_block = 0;
         int32_t col_block_next = first_col;
@@ -185,20 +190,21 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             break;
           }
           const uint32_t bar = full_bar + 8 * stage;
-          ptx::mbar_arrive_expect_tx(bar, Cfg::kTxBytes);
+          ptx::mbar_arrive_expect_tx(bar, kIsSdd ? Cfg::kTxBytes : Cfg::kBBytes + p.block_rows * Cfg::kTileK * 2);
           int32_t b_row;
           if (kIsSdd) {
             b_row = b_row_base + ks * Cfg::kTileK;
           } else {
-            const int32_t blk = begin + (ks >> 1);
-            const int32_t k_half = (ks & 1) * Cfg::kTileK;
-            ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * Cfg::kTileM, bar, stream_once);
-            if ((ks & 1) == 0) {
+            // A 128-row block spans two 64-wide K steps, a 64-row block one.
+            const int32_t blk = begin + (ks >> steps_shift);
+            const int32_t k_half = (ks & steps_mask) * Cfg::kTileK;
+            ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * p.block_rows, bar, stream_once);
+            if ((ks & steps_mask) == 0) {
               // The next block's column index is fetched one block ahead to keep it off the issue path.
               col_block = col_block_next;
               if (blk + 1 < end) col_block_next = p.col_indices[blk + 1];
             }
-            b_row = col_block * Cfg::kTileM + k_half;
+            b_row = col_block * p.block_rows + k_half;
           }
           const uint32_t b_dst = b_base + stage * Cfg::kBBytes;
 #pragma unroll
@@ -226,7 +232,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int32_t end = cur.end;
         cur = next;
         if (begin == end) continue;
-        const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) * 2;
+        const int32_t k_steps = kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) << steps_shift;
         if (!ptx::mbar_wait_bounded(acc_empty_bar + 8 * acc, acc_phase ^ 1u, abort_word)) {
           give_up(SB_DEV_TIMEOUT_MMA);
           break;
@@ -276,10 +282,12 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int32_t end = p.row_offsets[rb + 1];
       if (begin == end) {
         if (!kIsSdd && p.zero_dead_rows) {
-          uint4* dst = reinterpret_cast<uint4*>(p.y + (static_cast<int64_t>(rb) * Cfg::kTileM + row) * p.d_model + n0 +
+          uint4* dst = reinterpret_cast<uint4*>(p.y + (static_cast<int64_t>(rb) * out_rows + row) * p.d_model + n0 +
                                                 half * kHalfCols);
+          if (row < out_rows) {
 #pragma unroll
-          for (int q = 0; q < kHalfCols / 8; ++q) dst[q] = make_uint4(0u, 0u, 0u, 0u);
+            for (int q = 0; q < kHalfCols / 8; ++q) dst[q] = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
         continue;
       }
@@ -300,9 +308,10 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           // FFN column f lives in block begin + f/128, column f%128; 32 columns never straddle a block.
           dst = p.h_out + ((static_cast<int64_t>(begin) + (col >> 7)) * Cfg::kTileM + row) * 128 + (col & 127);
         } else {
-          dst = p.y + (static_cast<int64_t>(rb) * Cfg::kTileM + row) * p.d_model + col;
+          dst = p.y + (static_cast<int64_t>(rb) * out_rows + row) * p.d_model + col;
         }
         uint4* dst4 = reinterpret_cast<uint4*>(dst);
+        if (row >= out_rows) continue;  // 64-row blocks: the tile's upper half holds nothing to store
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint32_t packed[4];

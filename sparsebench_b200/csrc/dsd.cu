@@ -11,8 +11,6 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   clear_error();
   if (block_size != 64 && block_size != 128)
     return fail(SB_ERR_INVALID_ARGUMENT, "block size must be 64 or 128, got %d", block_size);
-  if (block_size == 64)
-    return fail(SB_ERR_UNSUPPORTED, "dsd: block size 64 is not built for sm_100a, only 128");
   if (d_model <= 0 || d_model % 128 != 0)
     return fail(SB_ERR_INVALID_ARGUMENT, "D (%d) must be a positive multiple of 128", d_model);
   if (w_rows <= 0 || w_rows % block_size != 0)
@@ -22,18 +20,19 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   if (!w || !row_offsets || !col_indices) return fail(SB_ERR_INVALID_ARGUMENT, "dsd: NULL buffer");
   if (!aligned16(h_blocks) || !aligned16(w) || !aligned16(y))
     return fail(SB_ERR_INVALID_ARGUMENT, "blocks, w and the output must be 16-byte aligned");
-  if (num_blocks * 128 > INT32_MAX || w_rows > INT32_MAX ||
-      static_cast<int64_t>(num_row_blocks) * 128 > INT32_MAX)
+  if (num_blocks * block_size > INT32_MAX || w_rows > INT32_MAX ||
+      static_cast<int64_t>(num_row_blocks) * block_size > INT32_MAX)
     return fail(SB_ERR_INVALID_ARGUMENT, "dsd: problem too large");
   if (num_row_blocks == 0) return SB_OK;
   if (!y) return fail(SB_ERR_INVALID_ARGUMENT, "dsd: NULL output");
 
   CUtensorMap map_a, map_b;
-  // H blocks [nnz, 128, 128] seen as [nnz*128, 128]; with no blocks at all every row block is dead
-  // and the map is never used, but it still has to be a valid descriptor.
+  // H blocks [nnz, bs, bs] seen as [nnz*bs, bs], one box = 64 K columns of one block; with no blocks
+  // at all every row block is dead and the map is never used, but it still has to be a valid
+  // descriptor.
   const void* a_base = (num_blocks > 0 && h_blocks) ? h_blocks : w;
-  const uint64_t a_rows = num_blocks > 0 ? static_cast<uint64_t>(num_blocks) * 128 : 128;
-  if (int rc = encode_bf16_2d_map(&map_a, a_base, a_rows, 128, 128, "dsd (blocks)")) return rc;
+  const uint64_t a_rows = num_blocks > 0 ? static_cast<uint64_t>(num_blocks) * block_size : block_size;
+  if (int rc = encode_bf16_2d_map(&map_a, a_base, a_rows, block_size, block_size, "dsd (blocks)")) return rc;
   if (int rc = encode_bf16_2d_map(&map_b, w, static_cast<uint64_t>(w_rows), static_cast<uint64_t>(d_model), 64,
                                   "dsd (w)"))
     return rc;
@@ -45,6 +44,7 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   params.col_indices = col_indices;
   params.y = static_cast<__nv_bfloat16*>(y);
   params.zero_dead_rows = zero_dead_rows ? 1 : 0;
+  params.block_rows = block_size;
   params.d_model = d_model;
   if (d_model % 256 == 0) {
     params.num_slices = d_model / 256;

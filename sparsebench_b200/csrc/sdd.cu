@@ -44,5 +44,6 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
   params.h_out = static_cast<__nv_bfloat16*>(h_blocks);
   params.apply_gelu = apply_gelu ? 1 : 0;
   params.d_model = d_model;
+  params.block_rows = 128;
   return launch_gemm<GemmOp::kSdd, 256>(map_a, map_b, params, as_stream(stream), "sdd");
 }

@@ -1,5 +1,5 @@
 """DSD (BSR(H) @ W) against the fp32 oracle (reference: tests/test_dsd.py). One tcgen05 kernel
-serves every `version`; block size 64 is not built and must say so."""
+serves every `version` and both block sizes (64-row blocks use half of the 128-row tile)."""
 
 import math
 
@@ -38,34 +38,39 @@ def oracle(blocks, w, layout):
 
 @pytest.mark.parametrize("version", [pytest.param(1, id="v1"), pytest.param(5, id="v5")])
 @pytest.mark.parametrize("case", CASE_NAMES)
+@pytest.mark.parametrize("bs", [64, 128])
 @pytest.mark.parametrize(("num_experts", "f_blocks"), [(8, 1), (8, 4), (64, 1), (64, 2)], ids=["E8F1", "E8F4", "E64F1", "E64F2"])
 @pytest.mark.parametrize("d_model", [128, 256, 512], ids=["D128", "D256", "D512"])
-def test_matches_oracle(version: int, case: str, num_experts: int, f_blocks: int, d_model: int) -> None:
-    if version == 5 and d_model % 256 != 0:
-        pytest.skip("v5 rejects D that is not a multiple of 256")
-    layout, blocks, w = make_inputs(case, 300, num_experts, f_blocks * 128, d_model, 128)
+def test_matches_oracle(version: int, case: str, bs: int, num_experts: int, f_blocks: int, d_model: int) -> None:
+    if version == 5 and (bs != 128 or d_model % 256 != 0):
+        pytest.skip("v5 rejects block size 64 and D that is not a multiple of 256")
+    layout, blocks, w = make_inputs(case, 300, num_experts, f_blocks * bs, d_model, bs)
     out = run(blocks, w, as_topology(layout), version)
     torch.testing.assert_close(out.float().cpu(), oracle(blocks, w, layout), **TOL)
 
 
 @pytest.mark.parametrize("version", VERSIONS)
-def test_single_token(version: int) -> None:
-    layout, blocks, w = make_inputs("random", 1, 8, 256, 256, 128)
+@pytest.mark.parametrize("bs", [64, 128])
+def test_single_token(version: int, bs: int) -> None:
+    if version == 5 and bs != 128:
+        pytest.skip("v5 rejects block size 64")
+    layout, blocks, w = make_inputs("random", 1, 8, 2 * bs, 256, bs)
     out = run(blocks, w, as_topology(layout), version)
     torch.testing.assert_close(out.float().cpu(), oracle(blocks, w, layout), **TOL)
 
 
+@pytest.mark.parametrize("bs", [64, 128])
 @pytest.mark.parametrize("d_model", [256, 384])
-def test_asymmetric_inputs(d_model: int) -> None:
+def test_asymmetric_inputs(d_model: int, bs: int) -> None:
     # reference: tests/test_dsd.py:86-102. No symmetry between rows and columns or between H and W.
-    layout, _, _ = make_inputs("random", 200, 8, 256, d_model, 128)
-    k_total = 8 * 256
+    layout, _, _ = make_inputs("random", 200, 8, 2 * bs, d_model, bs)
+    k_total = 8 * 2 * bs
     i = torch.arange(k_total, dtype=torch.float32)[:, None]
     j = torch.arange(d_model, dtype=torch.float32)[None, :]
     w = torch.sin(0.37 * i + 1.31 * j + 0.05 * i * j / d_model).bfloat16()
     p = torch.arange(layout.nnz_blocks, dtype=torch.float32)[:, None, None]
-    r = torch.arange(128, dtype=torch.float32)[None, :, None]
-    c = torch.arange(128, dtype=torch.float32)[None, None, :]
+    r = torch.arange(bs, dtype=torch.float32)[None, :, None]
+    c = torch.arange(bs, dtype=torch.float32)[None, None, :]
     blocks = (torch.cos(0.7 * r - 0.23 * c + 0.11 * p + 0.01 * r * c) / 16.0).bfloat16()
     out = run(blocks, w, as_topology(layout), 4)
     torch.testing.assert_close(out.float().cpu(), oracle(blocks, w, layout), **TOL)
@@ -149,10 +154,6 @@ def test_rejects_unsupported_block_size_and_version() -> None:
     blocks32 = torch.zeros(layout32.nnz_blocks, 32, 32, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="64 or 128"):
         _C.dsd_cuda(blocks32, w.cuda(), topo32.row_offsets, topo32.col_indices, 1)
-    # Legal for the reference, not built for sm_100a: says so instead of computing something else.
-    layout64, blocks64, w64 = make_inputs("random", 20, 4, 64, 256, 64)
-    with pytest.raises(RuntimeError, match="block size 64 is not built"):
-        run(blocks64, w64, as_topology(layout64), 1)
 
 
 @pytest.mark.parametrize(("bs", "d_model"), [(64, 256), (128, 128), (128, 384)])
