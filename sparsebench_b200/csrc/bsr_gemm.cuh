@@ -11,8 +11,9 @@
 //               swizzle) for both ops, A tiles (H blocks, K-major) for DSD.
 //   warp 1      lane 0: MMA issuer; the warp also owns the TMEM allocation (2 accumulators).
 //   warps 2-9   epilogue: tcgen05.ld of the finished accumulator (lane quarter = warp % 4, column
-//               half = (warp - 2) / 4), GELU for SDD, bf16 pack, 16-byte global stores. Runs on
-//               accumulator i while the MMA warp fills accumulator i^1.
+//               half = (warp - 2) / 4), GELU for SDD, bf16 pack into a per-warp swizzled staging tile
+//               (32 rows x 128 B) and one TMA store per 64 columns. Runs on accumulator i while
+//               the MMA warp fills accumulator i^1.
 //   warps 10-13 SDD only: A gather. Per K step each thread issues 8 cp.async of 16 bytes straight
 //               from x[row_token] into the swizzled K-major stage; eight lanes share a row, so a warp
 //               instruction moves four whole 128-byte row segments. Padding rows use the zero-fill
@@ -74,7 +75,8 @@ struct GemmConfig {
   static constexpr int kThreads = 32 * (kFirstGatherWarp + kGatherWarps);
   static constexpr int kTmemColumns = 2 * kTileN;              // two accumulators; 256 or 512
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarrierBytes;
+  static constexpr int kStagingBytes = 32 * 128;               // per epilogue warp: 32 rows x 64 bf16
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpilogueWarps * kStagingBytes + kBarrierBytes;
   static constexpr uint32_t kFullArrivals = kOp == GemmOp::kSdd ? 1 + 32 * kGatherWarps : 1;
   static constexpr uint32_t kTxBytes = kOp == GemmOp::kSdd ? kBBytes : kStageBytes;
   static_assert(kTileN == 128 || kTileN == 256, "tile width");
@@ -86,7 +88,7 @@ __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + e
 template <GemmOp kOp, int kTileN>
 __global__ void __launch_bounds__(GemmConfig<kOp, kTileN>::kThreads, 1)
 bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Cfg = GemmConfig<kOp, kTileN>;
   constexpr bool kIsSdd = kOp == GemmOp::kSdd;
 
@@ -94,7 +96,8 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + Cfg::kStages * Cfg::kABytes;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t staging_base = smem_base + Cfg::kStages * Cfg::kStageBytes;  // 1024-byte aligned
+  const uint32_t bar_base = staging_base + Cfg::kEpilogueWarps * Cfg::kStagingBytes;
   const uint32_t full_bar = bar_base;                              // [kStages]
   const uint32_t empty_bar = bar_base + 8 * Cfg::kStages;          // [kStages]
   const uint32_t acc_full_bar = bar_base + 16 * Cfg::kStages;      // [2]
@@ -122,6 +125,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     ptx::fence_barrier_init();
     if (!kIsSdd) ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
+    ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, Cfg::kTmemColumns);
@@ -144,8 +148,9 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   struct TileInfo {
     int32_t begin, end, expert;
   };
+  auto row_block_of = [&](int32_t tile) { return tile / p.num_slices; };
   auto load_tile_info = [&](int32_t tile) {
-    const int32_t rb = tile / p.num_slices;
+    const int32_t rb = row_block_of(tile);
     TileInfo info;
     info.begin = __ldg(p.row_offsets + rb);
     info.end = __ldg(p.row_offsets + rb + 1);
@@ -173,8 +178,8 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int32_t next_tile = tile + tile_step;
         const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0};
         int32_t next_first_col = 0;
-        const int32_t rb = tile / p.num_slices;
-        const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
+        const int32_t rb = row_block_of(tile);
+        const int32_t n0 = (tile % p.num_slices) * kTileN;
         const int32_t begin = cur.begin;
         const int32_t end = cur.end;
         const int32_t k_steps = begin == end ? 0 : (kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) << steps_shift);
@@ -274,10 +279,13 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int half = (warp - Cfg::kFirstEpilogueWarp) >> 2;
     const int row = quarter * 32 + lane;
     constexpr int kHalfCols = kTileN / 2;
+    const uint32_t staging = staging_base + static_cast<uint32_t>(warp - Cfg::kFirstEpilogueWarp) * Cfg::kStagingBytes;
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+    const uint32_t stage_row = staging + static_cast<uint32_t>(lane) * 128u;
     uint32_t acc = 0, acc_phase = 0;
     for (int32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      const int32_t rb = tile / p.num_slices;
-      const int32_t n0 = (tile - rb * p.num_slices) * kTileN;
+      const int32_t rb = row_block_of(tile);
+      const int32_t n0 = (tile % p.num_slices) * kTileN;
       const int32_t begin = p.row_offsets[rb];
       const int32_t end = p.row_offsets[rb + 1];
       if (begin == end) {
@@ -297,36 +305,46 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       ptx::tcgen05_fence_after_sync();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTileN + half * kHalfCols;
+      // 64 columns at a time: TMEM -> registers -> (GELU) -> bf16 -> this warp's swizzled staging
+      // tile [32 rows x 128 B] -> one TMA store, so global memory sees whole 128-byte row segments
+      // instead of 32 scattered 16-byte pieces per instruction.
 #pragma unroll 1
-      for (int cc = 0; cc < kHalfCols / 32; ++cc) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(t_addr + cc * 32, v);
-        ptx::tmem_ld_wait();
-        const int32_t col = n0 + half * kHalfCols + cc * 32;  // first of 32 output columns
-        __nv_bfloat16* dst;
-        if (kIsSdd) {
-          // FFN column f lives in block begin + f/128, column f%128; 32 columns never straddle a block.
-          dst = p.h_out + ((static_cast<int64_t>(begin) + (col >> 7)) * Cfg::kTileM + row) * 128 + (col & 127);
-        } else {
-          dst = p.y + (static_cast<int64_t>(rb) * out_rows + row) * p.d_model + col;
-        }
-        uint4* dst4 = reinterpret_cast<uint4*>(dst);
-        if (row >= out_rows) continue;  // 64-row blocks: the tile's upper half holds nothing to store
+      for (int g = 0; g < kHalfCols / 64; ++g) {
+        uint32_t packed[32];  // this lane's row: 64 columns as bf16 pairs
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t packed[4];
+        for (int part = 0; part < 2; ++part) {
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(t_addr + g * 64 + part * 32, v);
+          ptx::tmem_ld_wait();
 #pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            float f0 = __uint_as_float(v[q * 8 + 2 * h]);
-            float f1 = __uint_as_float(v[q * 8 + 2 * h + 1]);
+          for (int h = 0; h < 16; ++h) {
+            float f0 = __uint_as_float(v[2 * h]);
+            float f1 = __uint_as_float(v[2 * h + 1]);
             if (kIsSdd && p.apply_gelu) {
               f0 = gelu_erf(f0);
               f1 = gelu_erf(f1);
             }
             const __nv_bfloat162 pair = __floats2bfloat162_rn(f0, f1);
-            packed[h] = *reinterpret_cast<const uint32_t*>(&pair);
+            packed[part * 16 + h] = *reinterpret_cast<const uint32_t*>(&pair);
           }
-          dst4[q] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+        if (lane == 0) ptx::bulk_wait_read();  // the previous store has finished reading the staging tile
+        __syncwarp();
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c)
+          ptx::st_shared_v4(stage_row + ((c ^ swz) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2],
+                            packed[4 * c + 3]);
+        ptx::fence_proxy_async_shared();
+        __syncwarp();
+        if (lane == 0 && quarter * 32 < out_rows) {
+          const int32_t col = n0 + half * kHalfCols + g * 64;  // first of 64 output columns
+          if (kIsSdd) {
+            // FFN column f lives in block begin + f/128, column f%128; 64 columns never straddle a block.
+            ptx::tma_store_2d(&map_out, staging, col & 127, (begin + (col >> 7)) * Cfg::kTileM + quarter * 32);
+          } else {
+            ptx::tma_store_2d(&map_out, staging, col, rb * out_rows + quarter * 32);
+          }
+          ptx::bulk_commit();
         }
       }
       ptx::tcgen05_fence_before_sync();
@@ -334,6 +352,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) ptx::bulk_wait_all();  // this warp's stores are complete before the CTA retires
   } else if (kIsSdd) {
     // ---------------------------------------------------------------- A gather (SDD)
     // Lane l = (g, c): g = l >> 3 picks one of four rows, c = l & 7 the 16-byte chunk of the 128-byte
@@ -433,8 +452,8 @@ int prepare_gemm_kernel(int device) {
 }
 
 template <GemmOp kOp, int kTileN>
-int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& params, cudaStream_t stream,
-                const char* what) {
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out,
+                const GemmParams& params, cudaStream_t stream, const char* what) {
   int device = 0;
   const DeviceInfo* info = current_device_info(&device);
   if (info == nullptr) return SB_ERR_CUDA;
@@ -442,7 +461,7 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmPa
   using Cfg = GemmConfig<kOp, kTileN>;
   const int64_t tiles = static_cast<int64_t>(params.num_row_blocks) * params.num_slices;
   const unsigned grid = static_cast<unsigned>(tiles < info->sm_count ? tiles : info->sm_count);
-  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, params);
+  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, map_out, params);
   return check_launch(what);
 }
 

@@ -37,6 +37,11 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
                                   "dsd (w)"))
     return rc;
 
+  CUtensorMap map_out;  // y [num_row_blocks*bs, D]; the epilogue stores 32 x 64 boxes
+  if (int rc = encode_bf16_2d_map(&map_out, y, static_cast<uint64_t>(num_row_blocks) * block_size,
+                                  static_cast<uint64_t>(d_model), 32, "dsd (y)"))
+    return rc;
+
   GemmParams params{};
   params.row_offsets = row_offsets;
   params.num_row_blocks = num_row_blocks;
@@ -48,8 +53,8 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   params.d_model = d_model;
   if (d_model % 256 == 0) {
     params.num_slices = d_model / 256;
-    return launch_gemm<GemmOp::kDsd, 256>(map_a, map_b, params, as_stream(stream), "dsd");
+    return launch_gemm<GemmOp::kDsd, 256>(map_a, map_b, map_out, params, as_stream(stream), "dsd");
   }
   params.num_slices = d_model / 128;
-  return launch_gemm<GemmOp::kDsd, 128>(map_a, map_b, params, as_stream(stream), "dsd");
+  return launch_gemm<GemmOp::kDsd, 128>(map_a, map_b, map_out, params, as_stream(stream), "dsd");
 }

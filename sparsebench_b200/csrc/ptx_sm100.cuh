@@ -110,6 +110,30 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   return p;
 }
 
+// 2-D tiled store from this CTA's shared memory (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the issuing thread's bulk stores have finished READING shared memory (it may be reused).
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Until the issuing thread's bulk stores are complete.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// 16-byte global store with an L2 cache-policy operand.
+__device__ __forceinline__ void st_global_v4_hint(void* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                                  uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(addr), "r"(a), "r"(b), "r"(c),
+               "r"(d), "l"(policy)
+               : "memory");
+}
+
 // ---- cp.async (per-thread 16-byte copies, used for the gathered A rows of SDD) --------------------
 // Copies 16 bytes, or writes 16 zero bytes without touching global memory when `valid` is false.
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, bool valid) {

@@ -33,6 +33,11 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
                                   "sdd (w1)"))
     return rc;
 
+  // Output: the block list [nnz, 128, 128] seen as [nnz*128, 128]; the epilogue stores 32 x 64 boxes.
+  CUtensorMap map_out;
+  const uint64_t nnz = static_cast<uint64_t>(num_row_blocks) * (ffn_dim / 128);
+  if (int rc = encode_bf16_2d_map(&map_out, h_blocks, nnz * 128, 128, 32, "sdd (blocks)")) return rc;
+
   GemmParams params{};
   params.row_offsets = row_offsets;
   params.num_row_blocks = num_row_blocks;
@@ -45,5 +50,5 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
   params.apply_gelu = apply_gelu ? 1 : 0;
   params.d_model = d_model;
   params.block_rows = 128;
-  return launch_gemm<GemmOp::kSdd, 256>(map_a, map_b, params, as_stream(stream), "sdd");
+  return launch_gemm<GemmOp::kSdd, 256>(map_a, map_b, map_out, params, as_stream(stream), "sdd");
 }
