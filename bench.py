@@ -315,6 +315,17 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     }
     if not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(cfg, layer)
+    if cfg.name == "fine_grained" and not args.no_scaling_reference:
+        # The multi-GPU runs use the expert-parallel workload (E=128, D=F=2048); its one-GPU value is
+        # what their per-GPU throughput should be compared with, so it rides along on this line.
+        del dev, layer, graph, graph_out, out, h, y, topo
+        torch.cuda.empty_cache()
+        from sparsebench_b200 import ep_bench
+
+        short = argparse.Namespace(**{**vars(args), "workload": "expert_parallel", "steps": min(args.steps, 50)})
+        ep_line = ep_bench.measure(short, METRIC, measured_peaks(), ClockSampler, 1, 0, 0)
+        line["expert_parallel_1gpu"] = {k: ep_line[k] for k in ("value", "unit", "ms_per_step", "steps")}
+        line["expert_parallel_1gpu"]["workload"] = ep_line["config"]["workload"]
     print(json.dumps(line))
 
 
@@ -345,6 +356,8 @@ def main() -> None:
     parser.add_argument("--workload", default=None, choices=sorted(CONFIGS))
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-scaling-reference", action="store_true",
+                        help="skip the one-GPU run of the expert-parallel workload that rides along at N=1")
     parser.add_argument("--ep-capacity-factor", type=float, default=3.0,
                         help="expert-parallel exchange rows per rank pair, as a multiple of the even share T*k/N")
     parser.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],

@@ -51,13 +51,32 @@ def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int)
 
 
 def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -> None:
+    """Measures the expert-parallel step on every rank; rank 0 prints the JSON line."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    line = measure(args, metric, peaks, clock_sampler_cls, world, rank, local)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        # Leave without tearing the communicator down: destroying it while a captured graph still
+        # holds its collectives has been seen to block forever. Every rank has printed and
+        # synchronised by now, so a hard exit loses nothing.
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls, world: int, rank: int,
+            local: int) -> dict:
+    """One full measurement of the expert-parallel step; returns the JSON line (meaningful on rank 0)."""
+    device = torch.device("cuda", local)
     cfg = CONFIGS[args.workload or "expert_parallel"]
     if cfg.num_experts % world != 0:
         raise SystemExit(f"{cfg.num_experts} experts do not split over {world} ranks")
@@ -122,6 +141,10 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
             raise
         torch.cuda.synchronize()
 
+    # Kernels of this library per step: sort, plan, (pack | push counts + push rows + barrier),
+    # slot experts, routing (1 launch, 3 beyond 262144 slots), SDD, DSD, (pack | push rows + barrier), combine.
+    route_launches = 1 if world * moe.capacity <= 262144 else 3
+    launches_per_step = (12 if moe.peer is not None else 8) + route_launches
     with clock_sampler_cls(local) as clocks:
         ms_per_step = _timed_steps(step, flush, args.warmup, args.steps, world)
     value = world * cfg.useful_flops / (ms_per_step * 1e-3) / 1e12
@@ -191,30 +214,19 @@ def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -
                        "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},
     })
 
-    if rank == 0:
-        line = {
-            "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
-                       "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
-                       "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity, "exchange": exchange,
-                       "launch": launch, "l2": "256 MiB written before every step",
-                       "frac_of_bf16_peak": value / world / bf16_tflops},
-            "clocks": clocks.summary(),
-            "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": (9 + (2 if world * moe.capacity > 32768 else 0)) * args.steps,
-            "roofline": roofline,
-        }
-        print(json.dumps(line))
-    if world > 1:
-        # Leave without tearing the communicator down: destroying it while a captured graph still
-        # holds its collectives has been seen to block forever. Every rank has printed and
-        # synchronised by now, so a hard exit loses nothing.
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(0)
+    line = {
+        "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
+                   "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
+                   "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
+                   "exchange": exchange, "launch": launch, "l2": "256 MiB written before every step",
+                   "frac_of_bf16_peak": value / world / bf16_tflops},
+        "clocks": clocks.summary(),
+        "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline,
+    }
+    return line
