@@ -73,6 +73,23 @@ def test_sdd_asymmetric_inputs() -> None:
     torch.testing.assert_close(out.float().cpu(), expected(x, w1, layout, False), **TOL)
 
 
+def test_sdd_gelu_is_the_erf_form_to_bf16_rounding() -> None:
+    # One-hot token rows make every pre-activation an exact copy of a weight, so the only arithmetic
+    # left is the GELU itself: it must agree with the erf form (not the tanh form) to the last bf16
+    # bit or one next to it, over the whole range where GELU is not trivially 0 or x.
+    num_tokens, d_model, ffn_dim = 64, 64, 256
+    x = torch.eye(num_tokens, d_model).bfloat16()
+    w1 = torch.linspace(-7.0, 7.0, d_model * ffn_dim).reshape(1, d_model, ffn_dim).bfloat16()
+    idx = torch.zeros(num_tokens, 1, dtype=torch.int64)
+    layout = L.build_topology(idx, 1, ffn_dim, 128)
+    out = run_sdd(x, w1, as_topology(layout)).float().cpu()
+    want = torch.nn.functional.gelu(w1[0].float()).bfloat16().float()  # [64 tokens, 256]
+    got = out[:, :64, :].permute(1, 0, 2).reshape(64, ffn_dim)  # blocks [2,128,128] -> rows of tokens
+    torch.testing.assert_close(got, want, rtol=2**-7, atol=2e-6)
+    tanh_form = torch.nn.functional.gelu(w1[0].float(), approximate="tanh")
+    assert (got - want).abs().max() < (tanh_form - torch.nn.functional.gelu(w1[0].float())).abs().max()
+
+
 def test_sdd_worst_case_device_topology() -> None:
     # The no-sync path: worst-case buffers straight from route_device.
     from sparsebench_b200.routing import route_device
