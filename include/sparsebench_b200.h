@@ -161,6 +161,17 @@ int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gat
                int64_t num_tokens, int32_t k, int32_t d_model, sb_stream_t stream);
 
 /*
+ * Router front end: for every token the k largest of its num_experts logits (descending; the lower
+ * expert id wins among equal values) and a softmax over those k logits only, computed in fp32 and
+ * rounded to the logits' type. Replaces what the reference does on the host side with torch.topk +
+ * torch.softmax (sparsebench/reference.py:19-29); its outputs are exactly the expert_idx /
+ * expert_weight inputs of the layer. logits_dtype: 0 = bf16, 1 = fp32; expert_weight has the same
+ * type; expert_idx is int32 or int64 [T, k]. num_experts <= 1024, k <= min(num_experts, 8).
+ */
+int sb_router_topk(const void* logits, int logits_dtype, int64_t num_tokens, int32_t num_experts, int32_t k,
+                   void* expert_idx, int idx_is_i64, void* expert_weight, sb_stream_t stream);
+
+/*
  * The layer on a flat assignment list: copy c sends token token_of_copy[c] to expert
  * expert_of_copy[c] with weight weight_of_copy[c]; a token may have any number of copies,
  * including none. Replaces the PyTorch steps of sparsebench::moe_forward_assigned

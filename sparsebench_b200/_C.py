@@ -188,6 +188,25 @@ def combine_cuda(y: torch.Tensor, copy_row: torch.Tensor, expert_weight: torch.T
     return out
 
 
+# ---- router front end (torch.topk + softmax in the reference, sparsebench/reference.py:19-29) ----------
+
+def router_topk_cuda(logits: torch.Tensor, k: int, index_dtype: torch.dtype = torch.int64) -> tuple[torch.Tensor, torch.Tensor]:
+    """(expert_idx [T, k], expert_weight [T, k]): the k largest logits per token and a softmax over them."""
+    lib = _lib.load()
+    _check(logits.is_cuda and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous [T, E] CUDA tensor")
+    _check(logits.dtype in (torch.bfloat16, torch.float32), "logits must be bfloat16 or float32")
+    _check(index_dtype in (torch.int32, torch.int64), "index_dtype must be int32 or int64")
+    num_tokens, num_experts = logits.shape
+    _check(0 < k <= num_experts, f"need [T, E] logits with 0 < k <= E, got {tuple(logits.shape)} and k={k}")
+    with torch.cuda.device(logits.device):
+        idx = torch.empty((num_tokens, k), dtype=index_dtype, device=logits.device)
+        weight = torch.empty((num_tokens, k), dtype=logits.dtype, device=logits.device)
+        if num_tokens > 0:
+            _lib.check(lib.sb_router_topk(_ptr(logits), int(logits.dtype == torch.float32), num_tokens, num_experts, k,
+                                          _ptr(idx), int(index_dtype == torch.int64), _ptr(weight), _stream()))
+    return idx, weight
+
+
 # ---- the layer on a flat assignment list (PyTorch ops in the reference, sparsebench/moe.py:59-91) ---
 
 def remap_rows_cuda(row_copy: torch.Tensor, token_of_copy: torch.Tensor) -> torch.Tensor:

@@ -7,7 +7,7 @@ missing. There is no CPU or PyTorch fallback.
 """
 
 from sparsebench_b200.moe import moe_forward, moe_forward_assigned
-from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route_device
+from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route, route_device
 from sparsebench_b200.spmm import combine, dsd, sdd
 from sparsebench_b200.topology import Topology
 
@@ -19,6 +19,7 @@ __all__ = [
     "dsd",
     "moe_forward",
     "moe_forward_assigned",
+    "route",
     "route_device",
     "sdd",
 ]
