@@ -1,0 +1,28 @@
+"""bench.py's reference arm and argument handling run without a GPU: the JSON line has the keys the
+contract names."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_reference_arm_prints_the_contract_keys() -> None:
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--workload", "cpu_small",
+                           "--steps", "2", "--warmup", "1"], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["higher_is_better"] is True
+    assert line["config"]["workload"] == "cpu_small" and line["n_gpus"] == 1
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert line["value"] > 0 and line["ms_per_step"] > 0 and line["gpu_launches"] == 0
+
+
+def test_non_zero_ranks_of_the_reference_arm_do_no_work() -> None:
+    env = {"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1", "PATH": "/usr/bin:/bin"}
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
+                          capture_output=True, text=True, timeout=120, env={**__import__("os").environ, **env})
+    assert proc.returncode == 0 and proc.stdout.strip() == ""

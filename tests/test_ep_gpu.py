@@ -105,3 +105,51 @@ def test_single_rank_step_in_a_cuda_graph() -> None:
     expected = M.moe_reference(fresh.x.float(), fresh.expert_idx, fresh.expert_weight.float(), fresh.w1.float(),
                                fresh.w2.float())
     torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2)
+
+
+def test_barrier_gives_up_with_a_status_instead_of_hanging() -> None:
+    # Failure detection without a fault: a two-rank barrier whose "peer" (a second pad in this GPU's
+    # own memory that nothing ever writes) never arrives. The wait is bounded: the kernel returns
+    # after its limit with SB_EP_TIMEOUT in the status word, and the context stays usable.
+    import time
+
+    from sparsebench_b200 import _C
+
+    pads = torch.zeros(2, 2, dtype=torch.int32, device="cuda")  # pads[r] = rank r's pad; we are rank 0
+    peer_pads = torch.tensor([pads[0].data_ptr(), pads[1].data_ptr()], dtype=torch.int64, device="cuda")
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    _C.ep_barrier(peer_pads, pads[0], epoch, 0, status)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - started
+    assert int(status.item()) == 2, "SB_EP_TIMEOUT expected"
+    assert 1.0 < waited < 10.0
+    assert pads[0].tolist() == [1, 0] and pads[1].tolist() == [1, 0]  # we signalled both, rank 1 never did
+    assert int(epoch.item()) == 1
+    # The context is still healthy: a one-rank barrier completes at once.
+    status.zero_()
+    one = torch.tensor([pads[0].data_ptr()], dtype=torch.int64, device="cuda")
+    _C.ep_barrier(one, pads[0], epoch, 0, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(epoch.item()) == 2
+
+
+def test_push_rows_into_own_memory_matches_gather() -> None:
+    # World size 1 view of the peer exchange: pushing through a "peer" table that points at this
+    # GPU's own buffer must leave what the pack kernel leaves.
+    from sparsebench_b200 import _C
+
+    g = torch.Generator().manual_seed(4)
+    src = torch.randn(100, 256, generator=g).bfloat16().cuda()
+    index = torch.randint(-1, 100, (2 * 64,), generator=g, dtype=torch.int32).cuda()
+    # Two "ranks" whose buffers are two halves of one tensor; we are rank 1 of 2, capacity 64.
+    recv = torch.zeros(2, 2 * 64, 256, dtype=torch.bfloat16, device="cuda")
+    table = torch.tensor([recv[0].data_ptr(), recv[1].data_ptr()], dtype=torch.int64, device="cuda")
+    _C.ep_push_rows(src, index, table, 1, 64)
+    torch.cuda.synchronize()
+    packed = _C.gather_rows(src, index, torch.zeros(128, 256, dtype=torch.bfloat16, device="cuda"))
+    for peer in range(2):
+        assert torch.equal(recv[peer, 64:128], packed[peer * 64:(peer + 1) * 64])  # rows land at [my_rank=1][i]
+        assert torch.all(recv[peer, :64] == 0)
