@@ -1,10 +1,10 @@
 """Generates the golden fixtures in this folder by RUNNING THE REFERENCE ITSELF.
 
-Run once in a container that has the SparseBench tree (default /root/reference, or
-SPARSEBENCH_REFERENCE=<path>); the fixtures are committed, the reference is not and does not
-travel. Nothing else in the repository imports the reference.
+Run once on a machine that has a checkout of the SparseBench tree; the fixtures are committed, the
+reference is not and does not travel. Nothing else in the repository imports the reference.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the SparseBench checkout>
+    (or SPARSEBENCH_REFERENCE=<path> python tests/golden/make_golden.py)
 
 Writes
   topology_cases.npz   expert_idx and every Topology field of topology.build_topology for small
@@ -28,7 +28,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REFERENCE = os.environ.get("SPARSEBENCH_REFERENCE", "/root/reference")
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SPARSEBENCH_REFERENCE")
+if not REFERENCE or not os.path.isdir(os.path.join(REFERENCE, "sparsebench")):
+    raise SystemExit("usage: make_golden.py <path to the SparseBench checkout> (or set SPARSEBENCH_REFERENCE)")
 sys.path.insert(0, REFERENCE)
 
 from sparsebench import reference as ref  # noqa: E402

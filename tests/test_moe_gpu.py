@@ -105,7 +105,7 @@ def test_stage_marks_fire_in_order_and_change_nothing() -> None:
     assert torch.equal(marked, moe_forward(x, idx, weight, w1, w2))  # deterministic run to run
 
 
-@pytest.mark.parametrize("name", ["fine_grained", "fine_grained_zipf"])
+@pytest.mark.parametrize("name", ["fine_grained", "fine_grained_zipf", "mixtral_like", "expert_parallel"])
 def test_benchmark_configuration_full_size(name: str) -> None:
     # Full benchmark size. The fp32 CPU oracle of the whole layer takes ~0.5 s here; the layout is
     # checked bit-exactly in test_routing_gpu.py, this checks the numbers.
