@@ -173,9 +173,12 @@ def pipelined_e2e_ms(forward, host_inputs, weights, warmup: int, steps: int) -> 
     return start.elapsed_time(end) / steps
 
 
-def live_rows(expert_idx: torch.Tensor, num_experts: int) -> int:
+def live_rows(expert_idx: torch.Tensor, num_experts: int, granule: int = 128) -> int:
+    """Rows of the layout after rounding every expert's copies up to `granule`: 128 is what the tensor
+    cores execute (whole row blocks), 32 what SDD stores and DSD loads and stores in the layer (groups
+    of 32 rows that are all padding are skipped)."""
     counts = torch.bincount(expert_idx.reshape(-1), minlength=num_experts)
-    return int(((counts + 127) // 128 * 128).sum())
+    return int(((counts + granule - 1) // granule * granule).sum())
 
 
 def cpu_baseline(cfg: LayerConfig, layer, budget_s: float = 20.0) -> dict:
@@ -311,22 +314,25 @@ def run_single_gpu(args: argparse.Namespace) -> None:
 
     # ---- per-kernel durations, each launch timed alone with events on the launching stream -----------
     topo = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
-    h = sdd(dev.x, dev.w1, topo)
+    # As the layer runs them: padding-only groups of 32 rows neither stored nor loaded.
+    h = sdd(dev.x, dev.w1, topo, skip_padding_rows=True)
     w2_cat = dev.w2.view(cfg.num_experts * cfg.ffn_dim, cfg.d_model)
-    y = dsd(h, w2_cat, topo, version=5)
+    y = dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
     iters = max(5, min(args.steps, 50))
     stage_ms = {
         "routing": statistics.mean(time_each_ms(lambda: route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128), flush, 3, iters)),
-        "sdd": statistics.mean(time_each_ms(lambda: sdd(dev.x, dev.w1, topo), flush, 3, iters)),
-        "dsd": statistics.mean(time_each_ms(lambda: dsd(h, w2_cat, topo, version=5), flush, 3, iters)),
+        "sdd": statistics.mean(time_each_ms(lambda: sdd(dev.x, dev.w1, topo, skip_padding_rows=True), flush, 3, iters)),
+        "dsd": statistics.mean(time_each_ms(lambda: dsd(h, w2_cat, topo, version=5, skip_padding_rows=True), flush, 3,
+                                            iters)),
         "combine": statistics.mean(time_each_ms(lambda: combine(y, dev.expert_weight, topo), flush, 3, iters)),
     }
-    rows = live_rows(layer.expert_idx, cfg.num_experts)
+    rows = live_rows(layer.expert_idx, cfg.num_experts)            # executed by the tensor cores
+    rows_moved = live_rows(layer.expert_idx, cfg.num_experts, 32)  # stored / loaded
     n_copies = cfg.num_tokens * cfg.k
     weight_bytes = cfg.num_experts * cfg.d_model * cfg.ffn_dim * 2
     stage_bytes = {
-        "sdd": cfg.num_tokens * cfg.d_model * 2 + weight_bytes + rows * cfg.ffn_dim * 2,
-        "dsd": rows * cfg.ffn_dim * 2 + weight_bytes + rows * cfg.d_model * 2,
+        "sdd": cfg.num_tokens * cfg.d_model * 2 + weight_bytes + rows_moved * cfg.ffn_dim * 2,
+        "dsd": rows_moved * cfg.ffn_dim * 2 + weight_bytes + rows_moved * cfg.d_model * 2,
         "combine": n_copies * cfg.d_model * 2 + n_copies * 6 + cfg.num_tokens * cfg.d_model * 2,
     }
     stage_flops = {"sdd": 2 * n_copies * cfg.d_model * cfg.ffn_dim, "dsd": 2 * n_copies * cfg.d_model * cfg.ffn_dim}
@@ -344,7 +350,7 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     roofline.update({
         "kernel": f"bsr_gemm_kernel<{dominant}>", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
         "launch_ms": stage_ms[dominant], "algorithmic_bytes": stage_bytes[dominant], "live_rows": rows,
-        "traffic": NCU_TRAFFIC_BYTES.get((cfg.name, dominant)),
+        "rows_moved": rows_moved, "traffic": NCU_TRAFFIC_BYTES.get((cfg.name, dominant)),
         "stages_ms": stage_ms,
         "stages_frac_of_hbm_peak": {s: stage_bytes[s] / (stage_ms[s] * 1e-3) / 1e9 / hbm_gbs for s in stage_bytes},
         "stages_useful_tflops": {s: stage_flops[s] / (stage_ms[s] * 1e-3) / 1e12 for s in stage_flops},

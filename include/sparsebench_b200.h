@@ -132,11 +132,15 @@ int sb_route_static_scratch(const void* expert_idx, int idx_is_i64, int64_t n_co
  * x, w1 and h_blocks 16-byte aligned. Row blocks with row_offsets[rb] == row_offsets[rb+1] are
  * skipped and their blocks left unwritten. dev_status (may be NULL) receives sb_device_status
  * bits if a bounded device-side wait expires; it is only ever OR-ed into.
+ * skip_padding_rows (no reference counterpart; 0 gives the reference's output): for layouts whose
+ * padding rows sit at the end of each row block, as sb_route writes them, a group of 32 rows that is
+ * all padding is not stored (those rows of the blocks stay unwritten instead of 0), which saves
+ * their share of the H traffic. Pair it with sb_dsd's row_token argument.
  */
 int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
            const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
-           int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int32_t* dev_status,
-           sb_stream_t stream);
+           int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int skip_padding_rows,
+           int32_t* dev_status, sb_stream_t stream);
 
 /*
  * DSD: y[rb*bs + r][:] = sum over p in [row_offsets[rb], row_offsets[rb+1]) of
@@ -146,10 +150,14 @@ int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_
  * block uses the lower half of the 128-row tensor-core tile) and d_model % 128 == 0.
  * Rows of row blocks without blocks are left unwritten, or zeroed when zero_dead_rows != 0
  * (what the reference's versions 1-3 do).
+ * row_token (no reference counterpart; NULL gives the reference's behaviour): the layout's
+ * [num_row_blocks * block_size] row -> token table with padding rows (< 0) at the end of each row
+ * block. When given, a group of 32 rows that is all padding is neither read from h_blocks nor
+ * written to y (those rows of y stay unwritten).
  */
 int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
            const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks, int32_t block_size,
-           int zero_dead_rows, void* y, int32_t* dev_status, sb_stream_t stream);
+           int zero_dead_rows, const int32_t* row_token, void* y, int32_t* dev_status, sb_stream_t stream);
 
 /*
  * Combine: out[t][:] = bf16( sum_j float(y[copy_row[t*k+j]][:]) * float(gate[t][j]) ), products and

@@ -93,9 +93,12 @@ def _check_index(t: torch.Tensor, name: str) -> None:
 
 
 def sdd_cuda(x: torch.Tensor, w1: torch.Tensor, row_token: torch.Tensor, row_block_expert: torch.Tensor,
-             row_offsets: torch.Tensor, num_nnz: int, apply_gelu: bool) -> torch.Tensor:
+             row_offsets: torch.Tensor, num_nnz: int, apply_gelu: bool,
+             skip_padding_rows: bool = False) -> torch.Tensor:
     """Blocks [num_nnz, 128, 128] = (gelu)(x[row_token] @ w1[expert]) on the layout's blocks.
-    Reference: csrc/sdd.cu:123-170. Blocks of dead row blocks are left unwritten."""
+    Reference: csrc/sdd.cu:123-170. Blocks of dead row blocks are left unwritten; with
+    skip_padding_rows so are groups of 32 rows that are all padding (padding at the end of each row
+    block, as routing lays it out) instead of coming out 0."""
     lib = _lib.load()
     _check(x.is_cuda and w1.is_cuda and x.device == w1.device, "x and w1 must be on the same GPU (CUDA tensors)")
     _check(x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16, "x and w1 must be bfloat16")
@@ -120,7 +123,8 @@ def sdd_cuda(x: torch.Tensor, w1: torch.Tensor, row_token: torch.Tensor, row_blo
         if num_row_blocks > 0:
             _lib.check(lib.sb_sdd(_ptr(x), _ptr(w1), _ptr(row_token), _ptr(row_block_expert), _ptr(row_offsets),
                                   _ptr(out), x.shape[0], d_model, ffn_dim, w1.shape[0], num_row_blocks,
-                                  int(bool(apply_gelu)), _ptr(device_status(x.device)), _stream()))
+                                  int(bool(apply_gelu)), int(bool(skip_padding_rows)),
+                                  _ptr(device_status(x.device)), _stream()))
     return out
 
 
@@ -129,11 +133,13 @@ _DSD_ZERO_DEAD_ROWS = {1, 2, 21, 3, 31}
 
 
 def dsd_cuda(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, col_indices: torch.Tensor,
-             version: int) -> torch.Tensor:
+             version: int, row_token: torch.Tensor | None = None) -> torch.Tensor:
     """out [num_row_blocks*bs, D] = BSR(blocks, row_offsets, col_indices) @ w.
     Reference: csrc/dsd.cpp:27-80. `version` keeps the reference's meaning for what is observable:
     versions 1, 2, 21, 3, 31 zero the rows of row blocks without blocks, 4, 41 and 5 leave them
-    unwritten, 5 insists on block size 128 and D % 256 == 0; one tcgen05 kernel serves them all."""
+    unwritten, 5 insists on block size 128 and D % 256 == 0; one tcgen05 kernel serves them all.
+    With row_token (the layout's row -> token table, padding at the end of each row block), groups of
+    32 rows that are all padding are neither read nor written."""
     lib = _lib.load()
     _check(blocks.is_cuda and w.is_cuda, "blocks and w must be CUDA tensors")
     _check(blocks.device == w.device and row_offsets.device == w.device and col_indices.device == w.device,
@@ -157,13 +163,18 @@ def dsd_cuda(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, c
     if version == 5:
         _check(bs == 128 and d_model % 256 == 0,
                f"dsd v5 needs block size 128 and D a multiple of 256, got block size {bs}, D {d_model}")
+    if row_token is not None:
+        _check_index(row_token, "row_token")
+        _check(row_token.device == w.device and row_token.numel() == num_row_blocks * bs,
+               f"row_token must hold {num_row_blocks * bs} rows on the same GPU")
 
     with torch.cuda.device(w.device):
         out = torch.empty((num_row_blocks * bs, d_model), dtype=torch.bfloat16, device=w.device)
         if num_row_blocks > 0:
             _lib.check(lib.sb_dsd(_ptr(blocks), blocks.shape[0], _ptr(w), w.shape[0], d_model, _ptr(row_offsets),
                                   _ptr(col_indices), num_row_blocks, bs, int(version in _DSD_ZERO_DEAD_ROWS),
-                                  _ptr(out), _ptr(device_status(w.device)), _stream()))
+                                  _ptr(row_token) if row_token is not None else None, _ptr(out),
+                                  _ptr(device_status(w.device)), _stream()))
     return out
 
 

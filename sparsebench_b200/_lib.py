@@ -28,8 +28,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                          _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_route_static_scratch": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
                                         _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, _P, _P]),
-    "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P]),
+    "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, c_int, _P, _P]),
+    "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P, _P]),
     "sb_combine": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int32, c_int32, _P]),
     "sb_router_topk": (c_int, [_P, c_int, c_int64, c_int32, c_int32, _P, c_int, _P, _P]),
     "sb_remap_rows": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, _P]),

@@ -55,6 +55,10 @@ struct GemmParams {
   int32_t block_rows;               // BSR block size: 128, or 64 (the tile's upper 64 rows then idle)
   // both
   int32_t d_model;
+  // Padding rows sit at the END of every row block (the layout routing writes). When set, a group of
+  // 32 rows that is all padding is not stored by either op and not loaded by DSD: SDD needs
+  // row_token anyway, DSD reads it (same array) only for this.
+  int32_t skip_padding;
 };
 
 template <GemmOp kOp, int kTileN>
@@ -104,8 +108,9 @@ __device__ __forceinline__ float gelu_erf(float v) {
 
 template <GemmOp kOp, int kTileN>
 __global__ void __launch_bounds__(GemmConfig<kOp, kTileN>::kThreads, 1)
-bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_rows32,
+                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
+                const GemmParams p) {
   using Cfg = GemmConfig<kOp, kTileN>;
   constexpr bool kIsSdd = kOp == GemmOp::kSdd;
 
@@ -141,6 +146,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     *abort_word = 0u;
     ptx::fence_barrier_init();
     if (!kIsSdd) ptx::prefetch_tensormap(&map_a);
+    if (!kIsSdd && p.skip_padding) ptx::prefetch_tensormap(&map_a_rows32);
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_out);
   }
@@ -164,6 +170,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // then the expert) are off the critical path at every tile boundary.
   struct TileInfo {
     int32_t begin, end, expert;
+    int32_t groups;  // DSD with skip_padding: leading 32-row groups of the row block that hold real rows
   };
   auto row_block_of = [&](int32_t tile) { return tile / p.num_slices; };
   auto load_tile_info = [&](int32_t tile) {
@@ -172,6 +179,11 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     info.begin = __ldg(p.row_offsets + rb);
     info.end = __ldg(p.row_offsets + rb + 1);
     info.expert = kIsSdd ? __ldg(p.row_block_expert + rb) : 0;
+    info.groups = 0;
+    if (!kIsSdd && p.skip_padding) {
+      const int32_t* rows = p.row_token + static_cast<int64_t>(rb) * p.block_rows;
+      for (int32_t g = 0; g < p.block_rows / 32; ++g) info.groups += __ldg(rows + 32 * g) >= 0 ? 1 : 0;
+    }
     return info;
   };
   const int32_t tile_step = static_cast<int32_t>(gridDim.x);
@@ -189,11 +201,11 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       int32_t tile = blockIdx.x;
-      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0};
+      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0, 0};
       int32_t first_col = (!kIsSdd && cur.begin != cur.end) ? __ldg(p.col_indices + cur.begin) : 0;
       for (; ok && tile < total_tiles; tile += tile_step) {
         const int32_t next_tile = tile + tile_step;
-        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0};
+        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0, 0};
         int32_t next_first_col = 0;
         const int32_t rb = row_block_of(tile);
         const int32_t n0 = (tile % p.num_slices) * kTileN;
@@ -212,7 +224,8 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             break;
           }
           const uint32_t bar = full_bar + 8 * stage;
-          ptx::mbar_arrive_expect_tx(bar, kIsSdd ? Cfg::kTxBytes : Cfg::kBBytes + p.block_rows * Cfg::kTileK * 2);
+          const int32_t a_rows = (!kIsSdd && p.skip_padding) ? cur.groups * 32 : p.block_rows;
+          ptx::mbar_arrive_expect_tx(bar, kIsSdd ? Cfg::kTxBytes : Cfg::kBBytes + a_rows * Cfg::kTileK * 2);
           int32_t b_row;
           if (kIsSdd) {
             b_row = b_row_base + ks * Cfg::kTileK;
@@ -220,7 +233,16 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // A 128-row block spans two 64-wide K steps, a 64-row block one.
             const int32_t blk = begin + (ks >> steps_shift);
             const int32_t k_half = (ks & steps_mask) * Cfg::kTileK;
-            ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * p.block_rows, bar, stream_once);
+            if (p.skip_padding && a_rows < p.block_rows) {
+              // A row block that ends in padding: only its 32-row groups with real rows are fetched
+              // (map_a_rows32 is map_a with a 32-row box). The rest of the stage keeps whatever it
+              // held; those accumulator rows are never stored.
+              for (int32_t g = 0; g < cur.groups; ++g)
+                ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes + g * (32 * 128), &map_a_rows32, k_half,
+                                      blk * p.block_rows + g * 32, bar, stream_once);
+            } else {
+              ptx::tma_load_2d_hint(a_base + stage * Cfg::kABytes, &map_a, k_half, blk * p.block_rows, bar, stream_once);
+            }
             if ((ks & steps_mask) == 0) {
               // The next block's column index is fetched one block ahead to keep it off the issue path.
               col_block = col_block_next;
@@ -246,10 +268,10 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       int32_t tile = blockIdx.x;
-      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0};
+      TileInfo cur = tile < total_tiles ? load_tile_info(tile) : TileInfo{0, 0, 0, 0};
       for (; ok && tile < total_tiles; tile += tile_step) {
         const int32_t next_tile = tile + tile_step;
-        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0};
+        const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0, 0};
         const int32_t begin = cur.begin;
         const int32_t end = cur.end;
         cur = next;
@@ -316,6 +338,11 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         continue;
       }
+      // This warp's 32 rows are all padding iff their first row is (padding sits at the end). Read
+      // before the wait, so that the load is not on the path from "accumulator ready" to the stores.
+      const bool rows_live = !p.skip_padding ||
+                             (quarter * 32 < out_rows &&
+                              __ldg(p.row_token + static_cast<int64_t>(rb) * out_rows + quarter * 32) >= 0);
       if (!ptx::mbar_wait_bounded(acc_full_bar + 8 * acc, acc_phase, abort_word)) {
         give_up(SB_DEV_TIMEOUT_EPILOGUE);
         break;
@@ -326,7 +353,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       // tile [32 rows x 128 B] -> one TMA store, so global memory sees whole 128-byte row segments
       // instead of 32 scattered 16-byte pieces per instruction.
 #pragma unroll 1
-      for (int g = 0; g < kHalfCols / 64; ++g) {
+      for (int g = 0; rows_live && g < kHalfCols / 64; ++g) {
         uint32_t packed[32];  // this lane's row: 64 columns as bf16 pairs
 #pragma unroll
         for (int part = 0; part < 2; ++part) {
@@ -388,7 +415,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     bool ok = true;
     int32_t tile = blockIdx.x;
     int32_t tok[8];
-    TileInfo cur = TileInfo{0, 0, 0};
+    TileInfo cur = TileInfo{0, 0, 0, 0};
     if (tile < total_tiles) {
       load_tokens(tile, tok);
       cur = load_tile_info(tile);
@@ -397,7 +424,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       // The next tile's record and row -> token table are fetched while this tile is gathered.
       const int32_t next = tile + tile_step;
       int32_t tok_next[8];
-      TileInfo next_info = TileInfo{0, 0, 0};
+      TileInfo next_info = TileInfo{0, 0, 0, 0};
       if (next < total_tiles) {
         load_tokens(next, tok_next);
         next_info = load_tile_info(next);
@@ -469,8 +496,8 @@ int prepare_gemm_kernel(int device) {
 }
 
 template <GemmOp kOp, int kTileN>
-int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_out,
-                const GemmParams& params, cudaStream_t stream, const char* what) {
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, const CUtensorMap& map_b,
+                const CUtensorMap& map_out, const GemmParams& params, cudaStream_t stream, const char* what) {
   int device = 0;
   const DeviceInfo* info = current_device_info(&device);
   if (info == nullptr) return SB_ERR_CUDA;
@@ -478,7 +505,8 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
   using Cfg = GemmConfig<kOp, kTileN>;
   const int64_t tiles = static_cast<int64_t>(params.num_row_blocks) * params.num_slices;
   const unsigned grid = static_cast<unsigned>(tiles < info->sm_count ? tiles : info->sm_count);
-  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_b, map_out, params);
+  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_a_rows32, map_b, map_out,
+                                                                                  params);
   return check_launch(what);
 }
 

@@ -6,7 +6,8 @@
 
 extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
                       const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
-                      int32_t block_size, int zero_dead_rows, void* y, int32_t* dev_status, sb_stream_t stream) {
+                      int32_t block_size, int zero_dead_rows, const int32_t* row_token, void* y,
+                      int32_t* dev_status, sb_stream_t stream) {
   using namespace sb;
   clear_error();
   if (block_size != 64 && block_size != 128)
@@ -33,6 +34,12 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   const void* a_base = (num_blocks > 0 && h_blocks) ? h_blocks : w;
   const uint64_t a_rows = num_blocks > 0 ? static_cast<uint64_t>(num_blocks) * block_size : block_size;
   if (int rc = encode_bf16_2d_map(&map_a, a_base, a_rows, block_size, block_size, "dsd (blocks)")) return rc;
+  // With row_token given, row blocks that end in padding are fetched in 32-row boxes, only the
+  // groups that hold real rows.
+  CUtensorMap map_a_rows32 = map_a;
+  if (row_token != nullptr) {
+    if (int rc = encode_bf16_2d_map(&map_a_rows32, a_base, a_rows, block_size, 32, "dsd (blocks, 32 rows)")) return rc;
+  }
   if (int rc = encode_bf16_2d_map(&map_b, w, static_cast<uint64_t>(w_rows), static_cast<uint64_t>(d_model), 64,
                                   "dsd (w)"))
     return rc;
@@ -50,11 +57,13 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   params.y = static_cast<__nv_bfloat16*>(y);
   params.zero_dead_rows = zero_dead_rows ? 1 : 0;
   params.block_rows = block_size;
+  params.row_token = row_token;
+  params.skip_padding = row_token != nullptr ? 1 : 0;
   params.d_model = d_model;
   if (d_model % 256 == 0) {
     params.num_slices = d_model / 256;
-    return launch_gemm<GemmOp::kDsd, 256>(map_a, map_b, map_out, params, as_stream(stream), "dsd");
+    return launch_gemm<GemmOp::kDsd, 256>(map_a, map_a_rows32, map_b, map_out, params, as_stream(stream), "dsd");
   }
   params.num_slices = d_model / 128;
-  return launch_gemm<GemmOp::kDsd, 128>(map_a, map_b, map_out, params, as_stream(stream), "dsd");
+  return launch_gemm<GemmOp::kDsd, 128>(map_a, map_a_rows32, map_b, map_out, params, as_stream(stream), "dsd");
 }

@@ -7,7 +7,7 @@
 extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
                       const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model,
                       int32_t ffn_dim, int32_t num_experts, int32_t num_row_blocks, int apply_gelu,
-                      int32_t* dev_status, sb_stream_t stream) {
+                      int skip_padding_rows, int32_t* dev_status, sb_stream_t stream) {
   using namespace sb;
   clear_error();
   if (!x || !w1 || !row_token || !row_block_expert || !row_offsets)
@@ -48,7 +48,8 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
   params.row_block_expert = row_block_expert;
   params.h_out = static_cast<__nv_bfloat16*>(h_blocks);
   params.apply_gelu = apply_gelu ? 1 : 0;
+  params.skip_padding = skip_padding_rows ? 1 : 0;
   params.d_model = d_model;
   params.block_rows = 128;
-  return launch_gemm<GemmOp::kSdd, 256>(map_a, map_b, map_out, params, as_stream(stream), "sdd");
+  return launch_gemm<GemmOp::kSdd, 256>(map_a, map_a, map_b, map_out, params, as_stream(stream), "sdd");
 }

@@ -72,12 +72,12 @@ class CudaOps:
     def sdd(self, x, w1, topo):
         from sparsebench_b200.spmm import sdd
 
-        return sdd(x, w1, topo, gelu=True)
+        return sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
 
     def dsd(self, h, w2_cat, topo):
         from sparsebench_b200.spmm import dsd
 
-        return dsd(h, w2_cat, topo, version=5)
+        return dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
 
     def combine(self, y: torch.Tensor, copy_row: torch.Tensor, expert_weight: torch.Tensor) -> torch.Tensor:
         from sparsebench_b200 import _C

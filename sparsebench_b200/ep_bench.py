@@ -190,9 +190,12 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
 
     rows = int(moe.last.owner_layout.padded_offsets[-1].item())  # live padded rows on this rank
     received = int(moe.last.recv_counts.sum().item())
+    # SDD stores, and DSD loads and stores, whole groups of 32 rows only where one holds a real row.
+    per_expert = moe.last.recv_counts.sum(dim=0)
+    rows_moved = int(((per_expert + 31) // 32 * 32).sum().item())
     weight_bytes = per_rank * cfg.d_model * cfg.ffn_dim * 2
-    sdd_bytes = received * cfg.d_model * 2 + weight_bytes + rows * cfg.ffn_dim * 2
-    dsd_bytes = rows * cfg.ffn_dim * 2 + weight_bytes + rows * cfg.d_model * 2
+    sdd_bytes = received * cfg.d_model * 2 + weight_bytes + rows_moved * cfg.ffn_dim * 2
+    dsd_bytes = rows_moved * cfg.ffn_dim * 2 + weight_bytes + rows_moved * cfg.d_model * 2
     gemm_ms = {"sdd": stage_ms["SDD + GELU (fused)"], "dsd": stage_ms["DSD"]}
     gemm_bytes = {"sdd": sdd_bytes, "dsd": dsd_bytes}
     dominant = max(gemm_ms, key=gemm_ms.get)
@@ -208,7 +211,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     payload = (world - 1) / world * cfg.num_tokens * cfg.k * cfg.d_model * 2  # useful bytes per direction
     roofline.update({
         "kernel": f"bsr_gemm_kernel<{dominant}> on rank 0", "peak_source": peak_kind, "launch_ms": gemm_ms[dominant],
-        "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "traffic": None, "stages_ms": stage_ms,
+        "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "rows_moved": rows_moved, "traffic": None, "stages_ms": stage_ms,
         "all_to_all": {"useful_bytes_per_direction": payload,
                        "sent_bytes_per_direction": payload if moe.peer is not None else world * moe.capacity * cfg.d_model * 2,
                        "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},

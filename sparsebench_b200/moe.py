@@ -48,9 +48,11 @@ def moe_forward(
 
     topo = route_device(expert_idx, num_experts, ffn_dim, BLOCK_SIZE)
     mark("routing")
-    h = sdd(x, w1, topo, gelu=True)
+    # Padding rows (up to 127 per expert) are neither stored by SDD nor read or stored by DSD in
+    # whole groups of 32: nothing reads them, and H is the largest activation stream of the layer.
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
     mark("SDD + GELU (fused)")
-    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5)
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True)
     mark("DSD")
     out = combine(y, expert_weight, topo)
     mark("combine")
@@ -82,6 +84,6 @@ def moe_forward_assigned(
     token_of_copy = token_of_copy.contiguous()
     # With k = 1 routing's row_token holds copy indices (-1 for padding): map them to tokens.
     topo = dataclasses.replace(topo, row_token=_C.remap_rows_cuda(topo.row_token, token_of_copy))
-    h = sdd(x, w1, topo, gelu=True)
-    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5)
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True)
     return _C.combine_assigned_cuda(y, topo.copy_row, token_of_copy, weight_of_copy, num_tokens)
