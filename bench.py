@@ -47,7 +47,7 @@ from sparsebench_b200.workloads import CONFIGS, LayerConfig, make_layer  # noqa:
 METRIC = "moe_fwd_useful_tflops"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/bsr_gemm_kernel_fine_grained.md (same workload, same kernels).
-NCU_TRAFFIC_BYTES = {("fine_grained", "sdd"): 608.8e6, ("fine_grained", "dsd"): 640.7e6}
+NCU_TRAFFIC_BYTES = {("fine_grained", "sdd"): 576.8e6, ("fine_grained", "dsd"): 619.1e6}
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 FALLBACK_BF16_TFLOPS = 1590.0
 
