@@ -59,6 +59,7 @@ struct GemmParams {
   // 32 rows that is all padding is not stored by either op and not loaded by DSD: SDD needs
   // row_token anyway, DSD reads it (same array) only for this.
   int32_t skip_padding;
+  int32_t raster_rows;              // >= 1: row blocks per band of the tile walk
 };
 
 template <GemmOp kOp, int kTileN>
@@ -172,7 +173,26 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     int32_t begin, end, expert;
     int32_t groups;  // DSD with skip_padding: leading 32-row groups of the row block that hold real rows
   };
-  auto row_block_of = [&](int32_t tile) { return tile / p.num_slices; };
+  // Tile order. Tiles are walked in bands of `raster_rows` row blocks: inside a band the row block
+  // changes fastest, then the column slice (1 = plain row-block-major order). With a band of 8 the
+  // CTAs that run at the same time work on the same ~18 column slices of (mostly) one expert's
+  // weights for 8 row blocks at once, so a weight tile is fetched from HBM once and served from L2
+  // to the other row blocks. That matters when an expert has many row blocks and many column
+  // slices (SDD at F = 14336: a row-block-major wave covers only 2.6 row blocks, and W1 would be
+  // streamed from HBM once per 2.6 row blocks); with ~2 row blocks per expert the plain order
+  // already has both in flight together and is a little faster.
+  const int32_t band_tiles = p.raster_rows * p.num_slices;
+  auto row_block_of = [&](int32_t tile) {
+    const int32_t band = tile / band_tiles;
+    const int32_t first = band * p.raster_rows;
+    const int32_t height = min(p.raster_rows, p.num_row_blocks - first);
+    return first + (tile - band * band_tiles) % height;
+  };
+  auto slice_of = [&](int32_t tile) {
+    const int32_t band = tile / band_tiles;
+    const int32_t height = min(p.raster_rows, p.num_row_blocks - band * p.raster_rows);
+    return (tile - band * band_tiles) / height;
+  };
   auto load_tile_info = [&](int32_t tile) {
     const int32_t rb = row_block_of(tile);
     TileInfo info;
@@ -208,7 +228,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const TileInfo next = next_tile < total_tiles ? load_tile_info(next_tile) : TileInfo{0, 0, 0, 0};
         int32_t next_first_col = 0;
         const int32_t rb = row_block_of(tile);
-        const int32_t n0 = (tile % p.num_slices) * kTileN;
+        const int32_t n0 = slice_of(tile) * kTileN;
         const int32_t begin = cur.begin;
         const int32_t end = cur.end;
         const int32_t k_steps = begin == end ? 0 : (kIsSdd ? p.d_model / Cfg::kTileK : (end - begin) << steps_shift);
@@ -324,7 +344,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t acc = 0, acc_phase = 0;
     for (int32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int32_t rb = row_block_of(tile);
-      const int32_t n0 = (tile % p.num_slices) * kTileN;
+      const int32_t n0 = slice_of(tile) * kTileN;
       const int32_t begin = p.row_offsets[rb];
       const int32_t end = p.row_offsets[rb + 1];
       if (begin == end) {
@@ -407,7 +427,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t chunk = static_cast<uint32_t>(lane & 7);
     const uint32_t dst_off = static_cast<uint32_t>(row0) * 128u + ((chunk ^ static_cast<uint32_t>(row0 & 7)) << 4);
     auto load_tokens = [&](int32_t tile, int32_t (&tok)[8]) {
-      const int32_t* rows = p.row_token + static_cast<int64_t>(tile / p.num_slices) * Cfg::kTileM + row0;
+      const int32_t* rows = p.row_token + static_cast<int64_t>(row_block_of(tile)) * Cfg::kTileM + row0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) tok[j] = __ldg(rows + j * 16);
     };
@@ -503,10 +523,12 @@ int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, const
   if (info == nullptr) return SB_ERR_CUDA;
   if (int rc = prepare_gemm_kernel<kOp, kTileN>(device)) return rc;
   using Cfg = GemmConfig<kOp, kTileN>;
+  GemmParams launch_params = params;
+  if (launch_params.raster_rows < 1) launch_params.raster_rows = 1;
   const int64_t tiles = static_cast<int64_t>(params.num_row_blocks) * params.num_slices;
   const unsigned grid = static_cast<unsigned>(tiles < info->sm_count ? tiles : info->sm_count);
   bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_a_rows32, map_b, map_out,
-                                                                                  params);
+                                                                                  launch_params);
   return check_launch(what);
 }
 

@@ -57,6 +57,7 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   params.y = static_cast<__nv_bfloat16*>(y);
   params.zero_dead_rows = zero_dead_rows ? 1 : 0;
   params.block_rows = block_size;
+  params.raster_rows = 1;  // row-block-major: D/256 slices per row block keep an expert's row blocks in one wave
   params.row_token = row_token;
   params.skip_padding = row_token != nullptr ? 1 : 0;
   params.d_model = d_model;

@@ -47,6 +47,23 @@ def test_sdd_without_gelu() -> None:
     torch.testing.assert_close(out.float().cpu(), expected(x, w1, layout, False), **TOL)
 
 
+@pytest.mark.parametrize(("num_tokens", "num_experts"), [(1500, 2), (1300, 3), (4100, 4)])
+def test_sdd_many_row_blocks_per_expert(num_tokens: int, num_experts: int) -> None:
+    # At >= 4 row blocks per expert the kernel walks its tiles in bands of 8 row blocks (row block
+    # fastest, then column slice); the row-block counts here leave a short last band (24, 22, 66 + dead ones).
+    idx, x, w1 = make_inputs("zipf", num_tokens, num_experts, 128, 768)
+    layout = L.build_topology(idx, num_experts, 768, 128)
+    out = run_sdd(x, w1, as_topology(layout))
+    torch.testing.assert_close(out.float().cpu(), expected(x, w1, layout, True), **TOL)
+    from sparsebench_b200.routing import route_device
+    from sparsebench_b200.spmm import sdd
+
+    topo = route_device(idx.cuda(), num_experts, 768, 128)  # worst-case sized: dead row blocks at the end
+    blocks = sdd(x.cuda(), w1.cuda(), topo)
+    live = int(topo.row_offsets[-1])
+    assert torch.equal(blocks[:live], out[:live])
+
+
 def test_sdd_single_token_is_mostly_padding() -> None:
     # 1 token, 2 copies: each row block is 1 real row + 127 zero-filled ones.
     idx, x, w1 = make_inputs("random", 1, 8, 128, 256)
