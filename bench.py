@@ -257,7 +257,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
 def run_single_gpu(args: argparse.Namespace) -> None:
     from sparsebench_b200 import _C, moe_forward, route_device
     from sparsebench_b200.spmm import combine, dsd, sdd
-    from sparsebench_b200.timing import l2_flush_buffer, time_each_ms
+    from sparsebench_b200.timing import captured, l2_flush_buffer, time_each_ms
 
     cfg = CONFIGS[args.workload or "fine_grained"]
     torch.cuda.set_device(0)
@@ -319,13 +319,19 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     w2_cat = dev.w2.view(cfg.num_experts * cfg.ffn_dim, cfg.d_model)
     y = dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
     iters = max(5, min(args.steps, 50))
-    stage_ms = {
-        "routing": statistics.mean(time_each_ms(lambda: route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128), flush, 3, iters)),
-        "sdd": statistics.mean(time_each_ms(lambda: sdd(dev.x, dev.w1, topo, skip_padding_rows=True), flush, 3, iters)),
-        "dsd": statistics.mean(time_each_ms(lambda: dsd(h, w2_cat, topo, version=5, skip_padding_rows=True), flush, 3,
-                                            iters)),
-        "combine": statistics.mean(time_each_ms(lambda: combine(y, dev.expert_weight, topo), flush, 3, iters)),
+    # One CUDA graph per kernel: events around a replay see the kernel alone, without the host-side
+    # launch work an eager call puts between the two events.
+    stage_fns = {
+        "routing": lambda: route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128),
+        "sdd": lambda: sdd(dev.x, dev.w1, topo, skip_padding_rows=True),
+        "dsd": lambda: dsd(h, w2_cat, topo, version=5, skip_padding_rows=True),
+        "combine": lambda: combine(y, dev.expert_weight, topo),
     }
+    stage_ms = {}
+    for stage, fn in stage_fns.items():
+        graph, keep = captured(fn)
+        stage_ms[stage] = statistics.mean(time_each_ms(graph.replay, flush, 3, iters))
+        del graph, keep
     rows = live_rows(layer.expert_idx, cfg.num_experts)            # executed by the tensor cores
     rows_moved = live_rows(layer.expert_idx, cfg.num_experts, 32)  # stored / loaded
     n_copies = cfg.num_tokens * cfg.k
@@ -423,6 +429,9 @@ def main() -> None:
                         help="expert-parallel exchange rows per rank pair, as a multiple of the even share T*k/N")
     parser.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                         help="expert-parallel exchange: rows stored into peer memory by our kernels, or NCCL all-to-all")
+    parser.add_argument("--ep-unfused-return", action="store_true",
+                        help="N > 1, peer exchange: DSD writes y and a second kernel pushes it (default: the DSD "
+                             "epilogue stores the rows into the source ranks' buffers)")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

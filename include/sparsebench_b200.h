@@ -268,6 +268,21 @@ int sb_ep_push_counts(const int32_t* counts, int32_t* const* peer_counts, int32_
 int sb_ep_barrier(uint32_t* const* peer_pads, uint32_t* my_pad, uint32_t* epoch_word, int32_t my_rank,
                   int32_t num_ranks, int32_t* status, sb_stream_t stream);
 
+/*
+ * The owner's DSD and the return of its rows in ONE kernel (no reference counterpart: the reference
+ * is single-GPU). Same product as sb_dsd at block size 128, but row r of the layout is not written
+ * to a local y: with j = row_slot[r] = src * capacity + i (the receive slot the row was computed
+ * for; the owner's routing with k = 1 leaves exactly this table as row_token, < 0 for padding), the
+ * epilogue stores it into rank src's return buffer, peer_base[src] + (my_rank * capacity + i) *
+ * d_model elements, as whole 128-byte segments over NVLink while the tensor cores work on the next
+ * tile. Replaces sb_dsd + sb_ep_push_rows on the return leg; follow it with sb_ep_barrier. Groups of
+ * 32 rows that are all padding are neither loaded nor stored.
+ */
+int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
+                   const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
+                   const int32_t* row_slot, void* const* peer_base, int32_t my_rank, int32_t num_ranks,
+                   int32_t capacity, int32_t* dev_status, sb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -347,6 +347,32 @@ def ep_push_rows(src: torch.Tensor, index: torch.Tensor, peer_base: torch.Tensor
                                        src.shape[1] * src.element_size(), _stream()))
 
 
+def ep_dsd_push(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, col_indices: torch.Tensor,
+                row_slot: torch.Tensor, peer_base: torch.Tensor, my_rank: int, capacity: int) -> None:
+    """DSD whose epilogue stores row r of the layout into rank (row_slot[r] // capacity)'s buffer
+    (peer_base, an int64 device array of mapped base addresses) at row my_rank*capacity +
+    row_slot[r] % capacity: dsd_cuda + ep_push_rows as one kernel. Block size 128."""
+    lib = _lib.load()
+    _check(blocks.is_cuda and w.is_cuda and blocks.device == w.device, "blocks and w must be on the same GPU")
+    _check(blocks.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "blocks and w must be bfloat16")
+    _check(blocks.is_contiguous() and w.is_contiguous(), "blocks and w must be contiguous")
+    _check(blocks.dim() == 3 and tuple(blocks.shape[1:]) == (BLOCK, BLOCK), f"blocks must be [nnz, 128, 128], got {tuple(blocks.shape)}")
+    _check(w.dim() == 2 and w.shape[1] % 128 == 0, f"w must be [E*F, D] with D a multiple of 128, got {tuple(w.shape)}")
+    for t, name in ((row_offsets, "row_offsets"), (col_indices, "col_indices"), (row_slot, "row_slot")):
+        _check_index(t, name)
+    num_row_blocks = row_offsets.numel() - 1
+    _check(row_slot.numel() == num_row_blocks * BLOCK, f"row_slot must hold {num_row_blocks * BLOCK} rows")
+    _check(blocks.shape[0] == col_indices.numel(), "blocks and col_indices disagree")
+    _check(peer_base.is_cuda and peer_base.dtype == torch.int64 and peer_base.is_contiguous(),
+           "peer_base must be a contiguous int64 CUDA tensor of base addresses")
+    with torch.cuda.device(w.device):
+        if num_row_blocks > 0:
+            _lib.check(lib.sb_ep_dsd_push(_ptr(blocks), blocks.shape[0], _ptr(w), w.shape[0], w.shape[1],
+                                          _ptr(row_offsets), _ptr(col_indices), num_row_blocks, _ptr(row_slot),
+                                          _ptr(peer_base), my_rank, peer_base.numel(), capacity,
+                                          _ptr(device_status(w.device)), _stream()))
+
+
 def ep_push_counts(counts: torch.Tensor, peer_counts: torch.Tensor, my_rank: int, experts_per_rank: int) -> None:
     """counts[d*E_local + e] -> rank d's table (peer_counts[d]) at [my_rank*E_local + e]."""
     lib = _lib.load()

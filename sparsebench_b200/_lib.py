@@ -40,6 +40,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "sb_ep_push_rows": (c_int, [_P, _P, _P, c_int32, c_int32, c_int32, c_int32, _P]),
     "sb_ep_push_counts": (c_int, [_P, _P, c_int32, c_int32, c_int32, _P]),
     "sb_ep_barrier": (c_int, [_P, _P, _P, c_int32, c_int32, _P, _P]),
+    "sb_ep_dsd_push": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, _P, _P, c_int32, c_int32, c_int32,
+                               _P, _P]),
 }
 
 _lib: ctypes.CDLL | None = None

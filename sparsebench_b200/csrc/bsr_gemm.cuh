@@ -60,6 +60,12 @@ struct GemmParams {
   // row_token anyway, DSD reads it (same array) only for this.
   int32_t skip_padding;
   int32_t raster_rows;              // >= 1: row blocks per band of the tile walk
+  // DSD as the last step of an expert-parallel owner: instead of y, row r of the layout (receive slot
+  // j = row_token[r] = src * capacity + i) is stored into rank src's return buffer peer_out[src] at
+  // row my_rank * capacity + i, straight from the epilogue (peer memory over NVLink). Null = off.
+  void* const* peer_out;
+  int32_t my_rank;
+  int32_t capacity;
 };
 
 template <GemmOp kOp, int kTileN>
@@ -363,6 +369,16 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const bool rows_live = !p.skip_padding ||
                              (quarter * 32 < out_rows &&
                               __ldg(p.row_token + static_cast<int64_t>(rb) * out_rows + quarter * 32) >= 0);
+      // Expert-parallel return: where this lane's row goes (0 = nowhere: a padding row).
+      uint64_t row_dst = 0;
+      if (!kIsSdd && p.peer_out != nullptr && quarter * 32 < out_rows) {
+        const int32_t slot = __ldg(p.row_token + static_cast<int64_t>(rb) * out_rows + row);
+        if (slot >= 0) {
+          const int32_t src_rank = slot / p.capacity;
+          const int64_t dst_row = static_cast<int64_t>(p.my_rank) * p.capacity + (slot - src_rank * p.capacity);
+          row_dst = reinterpret_cast<uint64_t>(p.peer_out[src_rank]) + static_cast<uint64_t>(dst_row) * p.d_model * 2u;
+        }
+      }
       if (!ptx::mbar_wait_bounded(acc_full_bar + 8 * acc, acc_phase, abort_word)) {
         give_up(SB_DEV_TIMEOUT_EPILOGUE);
         break;
@@ -398,6 +414,22 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (uint32_t c = 0; c < 8; ++c)
           ptx::st_shared_v4(stage_row + ((c ^ swz) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2],
                             packed[4 * c + 3]);
+        if (!kIsSdd && p.peer_out != nullptr) {
+          // Eight lanes per row: every warp instruction stores four whole 128-byte row segments into
+          // the buffers of the ranks the rows came from.
+          __syncwarp();
+          const int32_t col = n0 + half * kHalfCols + g * 64;
+          const uint32_t chunk = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3);
+            const uint64_t dst = __shfl_sync(0xffffffffu, row_dst, r);
+            const uint4 val = ptx::ld_shared_v4(staging + static_cast<uint32_t>(r) * 128u + ((chunk ^ static_cast<uint32_t>(r & 7)) << 4));
+            if (dst != 0) *reinterpret_cast<uint4*>(dst + static_cast<uint64_t>(col + chunk * 8) * 2u) = val;
+          }
+          __syncwarp();  // the staging tile is free again
+          continue;
+        }
         ptx::fence_proxy_async_shared();
         __syncwarp();
         if (lane == 0 && quarter * 32 < out_rows) {

@@ -4,12 +4,20 @@
 
 #include "bsr_gemm.cuh"
 
-extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
-                      const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
-                      int32_t block_size, int zero_dead_rows, const int32_t* row_token, void* y,
-                      int32_t* dev_status, sb_stream_t stream) {
-  using namespace sb;
-  clear_error();
+namespace sb {
+namespace {
+
+// Where the result rows go when they do not go to y: the expert-parallel return (see GemmParams).
+struct PeerReturn {
+  void* const* peer_out = nullptr;
+  int32_t my_rank = 0;
+  int32_t capacity = 0;
+};
+
+int dsd_launch(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
+               const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks, int32_t block_size,
+               int zero_dead_rows, const int32_t* row_token, void* y, const PeerReturn& peer, int32_t* dev_status,
+               sb_stream_t stream) {
   if (block_size != 64 && block_size != 128)
     return fail(SB_ERR_INVALID_ARGUMENT, "block size must be 64 or 128, got %d", block_size);
   if (d_model <= 0 || d_model % 128 != 0)
@@ -25,7 +33,7 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
       static_cast<int64_t>(num_row_blocks) * block_size > INT32_MAX)
     return fail(SB_ERR_INVALID_ARGUMENT, "dsd: problem too large");
   if (num_row_blocks == 0) return SB_OK;
-  if (!y) return fail(SB_ERR_INVALID_ARGUMENT, "dsd: NULL output");
+  if (!y && peer.peer_out == nullptr) return fail(SB_ERR_INVALID_ARGUMENT, "dsd: NULL output");
 
   CUtensorMap map_a, map_b;
   // H blocks [nnz, bs, bs] seen as [nnz*bs, bs], one box = 64 K columns of one block; with no blocks
@@ -44,10 +52,12 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
                                   "dsd (w)"))
     return rc;
 
-  CUtensorMap map_out;  // y [num_row_blocks*bs, D]; the epilogue stores 32 x 64 boxes
-  if (int rc = encode_bf16_2d_map(&map_out, y, static_cast<uint64_t>(num_row_blocks) * block_size,
-                                  static_cast<uint64_t>(d_model), 32, "dsd (y)"))
-    return rc;
+  CUtensorMap map_out = map_b;  // y [num_row_blocks*bs, D]; the epilogue stores 32 x 64 boxes (unused with a peer return)
+  if (y != nullptr) {
+    if (int rc = encode_bf16_2d_map(&map_out, y, static_cast<uint64_t>(num_row_blocks) * block_size,
+                                    static_cast<uint64_t>(d_model), 32, "dsd (y)"))
+      return rc;
+  }
 
   GemmParams params{};
   params.row_offsets = row_offsets;
@@ -57,6 +67,9 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   params.y = static_cast<__nv_bfloat16*>(y);
   params.zero_dead_rows = zero_dead_rows ? 1 : 0;
   params.block_rows = block_size;
+  params.peer_out = peer.peer_out;
+  params.my_rank = peer.my_rank;
+  params.capacity = peer.capacity;
   params.raster_rows = 1;  // row-block-major: D/256 slices per row block keep an expert's row blocks in one wave
   params.row_token = row_token;
   params.skip_padding = row_token != nullptr ? 1 : 0;
@@ -67,4 +80,33 @@ extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, i
   }
   params.num_slices = d_model / 128;
   return launch_gemm<GemmOp::kDsd, 128>(map_a, map_a_rows32, map_b, map_out, params, as_stream(stream), "dsd");
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
+                      const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
+                      int32_t block_size, int zero_dead_rows, const int32_t* row_token, void* y,
+                      int32_t* dev_status, sb_stream_t stream) {
+  sb::clear_error();
+  return sb::dsd_launch(h_blocks, num_blocks, w, w_rows, d_model, row_offsets, col_indices, num_row_blocks, block_size,
+                        zero_dead_rows, row_token, y, sb::PeerReturn{}, dev_status, stream);
+}
+
+extern "C" int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
+                              const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
+                              const int32_t* row_slot, void* const* peer_base, int32_t my_rank, int32_t num_ranks,
+                              int32_t capacity, int32_t* dev_status, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!row_slot || !peer_base) return fail(SB_ERR_INVALID_ARGUMENT, "ep_dsd_push: NULL buffer");
+  if (num_ranks <= 0 || my_rank < 0 || my_rank >= num_ranks || capacity <= 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_dsd_push: need 0 <= rank < ranks and capacity > 0");
+  PeerReturn peer;
+  peer.peer_out = peer_base;
+  peer.my_rank = my_rank;
+  peer.capacity = capacity;
+  return dsd_launch(h_blocks, num_blocks, w, w_rows, d_model, row_offsets, col_indices, num_row_blocks, 128, 0, row_slot,
+                    nullptr, peer, dev_status, stream);
 }

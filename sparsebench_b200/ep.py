@@ -94,6 +94,13 @@ class CudaOps:
 
         _C.ep_push_counts(counts, peer_counts, my_rank, experts_per_rank)
 
+    def dsd_push(self, h, w2_cat, topo, peer_base, my_rank, capacity) -> None:
+        """dsd + push_rows of the result as one kernel: the DSD epilogue stores every row into the
+        buffer of the rank it came from (topo.row_token is the owner's row -> receive slot table)."""
+        from sparsebench_b200 import _C
+
+        _C.ep_dsd_push(h, w2_cat, topo.row_offsets, topo.col_indices, topo.row_token, peer_base, my_rank, capacity)
+
     def barrier(self, peer_pads, my_pad, epoch, my_rank, status) -> None:
         from sparsebench_b200 import _C
 
@@ -163,12 +170,15 @@ class ExpertParallelMoE:
 
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
                  group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
-                 exchange: str = "nccl") -> None:
+                 exchange: str = "nccl", fuse_return: bool = True) -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
         (source, destination) pair; None means T*k of the first call's batch (never overflows).
         `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
         "peer" = rows stored straight into the owner's mapped memory by this library's kernels, with a
-        device-side barrier (only real rows travel; needs `capacity` up front and world size > 1)."""
+        device-side barrier (only real rows travel; needs `capacity` up front and world size > 1).
+        `fuse_return` (peer exchange only): the owner's DSD stores its rows straight into the source
+        ranks' buffers from its epilogue instead of writing y and pushing it with a second kernel."""
+        self.fuse_return = fuse_return
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -262,9 +272,15 @@ class ExpertParallelMoE:
         mark("routing")
         h = ops.sdd(peer.recv, self.w1, topo)
         mark("SDD + GELU (fused)")
-        y = ops.dsd(h, self.w2_cat, topo)
-        mark("DSD")
-        ops.push_rows(y, topo.copy_row, peer.peer_ret, self.rank, capacity)
+        if self.fuse_return and hasattr(ops, "dsd_push"):
+            # The DSD epilogue stores each row into its source rank's buffer: the return leg travels
+            # over NVLink while the tensor cores work, and y never exists.
+            ops.dsd_push(h, self.w2_cat, topo, peer.peer_ret, self.rank, capacity)
+            mark("DSD")
+        else:
+            y = ops.dsd(h, self.w2_cat, topo)
+            mark("DSD")
+            ops.push_rows(y, topo.copy_row, peer.peer_ret, self.rank, capacity)
         ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)
         mark("return all-to-all")
         out = ops.combine(peer.ret, return_row, expert_weight)

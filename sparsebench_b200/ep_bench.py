@@ -96,7 +96,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         # Rows stored straight into the owner's memory: only real rows travel, so the capacity can be
         # the exact worst case. If the buffers cannot be mapped on this machine every rank falls back.
         try:
-            moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer")
+            moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
+                                    fuse_return=not getattr(args, "ep_unfused_return", False))
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line
             mapped = torch.zeros(1, device=device)
@@ -142,9 +143,10 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         torch.cuda.synchronize()
 
     # Kernels of this library per step: sort, plan, (pack | push counts + push rows + barrier),
-    # slot experts, routing (1 launch, 3 beyond 262144 slots), SDD, DSD, (pack | push rows + barrier), combine.
+    # slot experts, routing (1 launch, 3 beyond 262144 slots), SDD, DSD, (pack | [push rows +] barrier), combine.
     route_launches = 1 if world * moe.capacity <= 262144 else 3
-    launches_per_step = (12 if moe.peer is not None else 8) + route_launches
+    fused_return = moe.peer is not None and moe.fuse_return
+    launches_per_step = (12 if moe.peer is not None else 8) + route_launches - (1 if fused_return else 0)
     with clock_sampler_cls(local) as clocks:
         ms_per_step = _timed_steps(step, flush, args.warmup, args.steps, world)
     value = world * cfg.useful_flops / (ms_per_step * 1e-3) / 1e12
@@ -224,7 +226,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
                    "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
                    "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
-                   "exchange": exchange, "launch": launch, "l2": "256 MiB written before every step",
+                   "exchange": exchange, "return_leg": "stored by the DSD epilogue" if fused_return else "separate kernel",
+                   "launch": launch, "l2": "256 MiB written before every step",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
         "clocks": clocks.summary(),
         "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,

@@ -37,3 +37,19 @@ def time_each_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: i
 def time_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: int = 3, iters: int = 20) -> float:
     """Median GPU time of fn() in ms."""
     return statistics.median(time_each_ms(fn, flush, warmup, iters))
+
+
+def captured(fn: Callable[[], object]) -> tuple[torch.cuda.CUDAGraph, object]:
+    """fn() captured into a CUDA graph (after one eager call on a side stream, so that one-time
+    set-up stays outside the capture). Returns (graph, fn's result): keep the result alive as long as
+    the graph is replayed. Replaying puts the kernels on the GPU with no host work in between, so
+    events around graph.replay() time the kernels and not the Python and driver calls that launch them."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        result = fn()
+    return graph, result

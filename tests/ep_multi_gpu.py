@@ -1,7 +1,10 @@
 """Expert-parallel parity on 2, 4 or 8 GPUs. Not collected by pytest; run it with torchrun:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/ep_multi_gpu.py [nccl|peer]
+        --master-port 29511 tests/ep_multi_gpu.py [nccl|peer|peer_unfused]
+
+(peer: the owner's DSD stores its rows into the source ranks' buffers from its epilogue;
+peer_unfused: DSD writes y and a second kernel pushes it.)
 
 Every rank builds the same global batch from a seed, keeps its T tokens and its E/N experts, runs
 one expert-parallel step eagerly and one through a CUDA graph with fresh tokens and routing, and
@@ -46,9 +49,10 @@ def main() -> None:
     g = torch.Generator().manual_seed(0)
     w1 = (torch.randn(E, D, F, generator=g) / D**0.5).bfloat16()
     w2 = (torch.randn(E, F, D, generator=g) / F**0.5).bfloat16()
-    exchange = sys.argv[1] if len(sys.argv) > 1 else "nccl"
+    mode = sys.argv[1] if len(sys.argv) > 1 else "nccl"
+    exchange = "peer" if mode.startswith("peer") else mode
     layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
-                              capacity=T * K, exchange=exchange)
+                              capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused")
     mine = slice(rank * T, (rank + 1) * T)
 
     def check(out: torch.Tensor, x, idx, gate, what: str) -> None:
@@ -109,7 +113,7 @@ def main() -> None:
 
     assert int(_C.device_status(torch.device("cuda", local)).item()) == 0
     layer.check()
-    print(f"rank {rank}/{world}: expert-parallel parity ok, exchange {exchange} "
+    print(f"rank {rank}/{world}: expert-parallel parity ok, exchange {mode} "
           f"(graph replay {'ok' if graph_ok else 'not captured'})", flush=True)
     # Hard exit after a last barrier: destroying the communicator while a captured graph still holds
     # its collectives has been seen to block forever.

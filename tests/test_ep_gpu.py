@@ -153,3 +153,39 @@ def test_push_rows_into_own_memory_matches_gather() -> None:
     for peer in range(2):
         assert torch.equal(recv[peer, 64:128], packed[peer * 64:(peer + 1) * 64])  # rows land at [my_rank=1][i]
         assert torch.all(recv[peer, :64] == 0)
+
+
+@pytest.mark.parametrize("case", ["zipf", "empty_middle"])
+def test_dsd_push_into_own_memory_matches_dsd_then_push(case: str) -> None:
+    # The fused return leg on one GPU: two "ranks" whose return buffers are two halves of one local
+    # tensor. The rows the DSD epilogue stores must be the rows dsd + ep_push_rows leave, bit for bit,
+    # and nothing else may be touched.
+    from sparsebench_b200 import _C
+    from sparsebench_b200.routing import route_device
+    from sparsebench_b200.spmm import dsd, sdd
+    from sparsebench_b200.workloads import routing_case
+
+    ranks, capacity, experts, d_model, ffn_dim, my_rank = 2, 192, 4, 256, 512, 1
+    g = torch.Generator().manual_seed(7)
+    slots = ranks * capacity
+    x = torch.randn(slots, d_model, generator=g).bfloat16().cuda()
+    w1 = (torch.randn(experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16().cuda()
+    w2 = (torch.randn(experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
+    slot_expert = routing_case(case, slots, experts, seed=3)[:, :1].clone()
+    slot_expert[torch.rand(slots, 1, generator=g) < 0.3] = -1  # empty receive slots
+    topo = route_device(slot_expert.to(torch.int32).cuda(), experts, ffn_dim, 128)
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
+    w2_cat = w2.view(experts * ffn_dim, d_model)
+
+    def buffers():
+        ret = torch.full((ranks, ranks * capacity, d_model), 7.0, dtype=torch.bfloat16, device="cuda")
+        return ret, torch.tensor([ret[r].data_ptr() for r in range(ranks)], dtype=torch.int64, device="cuda")
+
+    want, table = buffers()
+    y = dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
+    _C.ep_push_rows(y, topo.copy_row, table, my_rank, capacity)
+    got, table2 = buffers()
+    _C.ep_dsd_push(h, w2_cat, topo.row_offsets, topo.col_indices, topo.row_token, table2, my_rank, capacity)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    assert bool((want != 7.0).any())
