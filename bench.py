@@ -432,6 +432,9 @@ def main() -> None:
     parser.add_argument("--ep-unfused-return", action="store_true",
                         help="N > 1, peer exchange: DSD writes y and a second kernel pushes it (default: the DSD "
                              "epilogue stores the rows into the source ranks' buffers)")
+    parser.add_argument("--ep-micro-batches", type=int, default=0,
+                        help="N > 1, peer exchange: cut each step into this many pipelined micro-batches "
+                             "(0 = the default for this N)")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)

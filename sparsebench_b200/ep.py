@@ -170,15 +170,23 @@ class ExpertParallelMoE:
 
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
                  group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
-                 exchange: str = "nccl", fuse_return: bool = True) -> None:
+                 exchange: str = "nccl", fuse_return: bool = True, micro_batches: int = 1) -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
         (source, destination) pair; None means T*k of the first call's batch (never overflows).
         `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
         "peer" = rows stored straight into the owner's mapped memory by this library's kernels, with a
         device-side barrier (only real rows travel; needs `capacity` up front and world size > 1).
         `fuse_return` (peer exchange only): the owner's DSD stores its rows straight into the source
-        ranks' buffers from its epilogue instead of writing y and pushing it with a second kernel."""
+        ranks' buffers from its epilogue instead of writing y and pushing it with a second kernel.
+        `micro_batches` (peer exchange only): the T local tokens are cut into that many equal parts, each
+        a complete step with its own exchange buffers on its own stream, ordered so that part m+1 is
+        dispatched while part m is computed and part m returns while part m+1 is computed. Same result
+        bit for bit; every part reads the owner's expert weights again, so it pays only where the
+        owner's matmuls are tensor-bound (many tokens per expert) and the exchange is a large share."""
         self.fuse_return = fuse_return
+        self.micro_batches = int(micro_batches)
+        if self.micro_batches < 1:
+            raise ValueError("micro_batches must be >= 1")
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -196,11 +204,25 @@ class ExpertParallelMoE:
         if exchange not in ("nccl", "peer"):
             raise ValueError(f"exchange must be 'nccl' or 'peer', got {exchange!r}")
         self.peer: PeerExchange | None = None
+        self.part_peers: list[PeerExchange] = []
+        self.part_streams: list[torch.cuda.Stream] = []
         if exchange == "peer" and self.world > 1:
             if capacity is None:
                 raise ValueError("the peer exchange sizes its buffers at construction: pass `capacity`")
-            self.peer = PeerExchange(group if group is not None else dist.group.WORLD, w1_local.device, capacity,
-                                     d_model, experts_local, w1_local.dtype)
+            pg = group if group is not None else dist.group.WORLD
+            if self.micro_batches == 1:
+                self.peer = PeerExchange(pg, w1_local.device, capacity, d_model, experts_local, w1_local.dtype)
+            else:
+                if capacity % self.micro_batches:
+                    raise ValueError(f"capacity {capacity} does not split into {self.micro_batches} micro-batches")
+                self.part_capacity = capacity // self.micro_batches
+                for _ in range(self.micro_batches):
+                    self.part_peers.append(PeerExchange(pg, w1_local.device, self.part_capacity, d_model, experts_local,
+                                                        w1_local.dtype))
+                    self.part_streams.append(torch.cuda.Stream(device=w1_local.device))
+                self.peer = self.part_peers[0]
+        elif self.micro_batches != 1:
+            raise ValueError("micro_batches needs the peer exchange and more than one rank")
 
     def _all_to_all(self, send: torch.Tensor) -> torch.Tensor:
         """[N, ...] -> [N, ...]: block d goes to rank d, block s of the result came from rank s."""
@@ -225,19 +247,53 @@ class ExpertParallelMoE:
         num_tokens, k = expert_idx.shape
         if x.shape != (num_tokens, self.d_model) or expert_weight.shape != expert_idx.shape:
             raise ValueError("x must be [T, D] and expert_idx / expert_weight [T, k]")
+        if self.part_peers:
+            return self._forward_pipelined(x, expert_idx, expert_weight, mark)
+        return self._forward_part(x, expert_idx, expert_weight, mark, self.peer, self.capacity, None)
+
+    def _forward_pipelined(self, x, expert_idx, expert_weight, mark) -> torch.Tensor:
+        """The step as `micro_batches` independent part-steps on their own streams (forked from and
+        joined back into the caller's stream, so it captures into one graph). Part m+1 may not start
+        its dispatch before part m's rows have arrived (the two would only share the links), but
+        does not wait for part m's matmuls: that is where the overlap comes from."""
+        parts = self.micro_batches
+        num_tokens = x.shape[0]
+        if num_tokens % parts:
+            raise ValueError(f"{num_tokens} tokens do not split into {parts} micro-batches")
+        step = num_tokens // parts
+        main = torch.cuda.current_stream()
+        outs: list[torch.Tensor] = []
+        dispatched: torch.cuda.Event | None = None
+        for m, (peer, stream) in enumerate(zip(self.part_peers, self.part_streams)):
+            rows = slice(m * step, (m + 1) * step)
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                if dispatched is not None:
+                    stream.wait_event(dispatched)
+                arrived = torch.cuda.Event()
+                out = self._forward_part(x[rows], expert_idx[rows], expert_weight[rows], mark if m == 0 else _no_mark,
+                                         peer, self.part_capacity, arrived.record)
+                out.record_stream(main)
+            outs.append(out)
+            dispatched = arrived
+        for stream in self.part_streams:
+            main.wait_stream(stream)
+        return torch.cat(outs)
+
+    def _forward_part(self, x, expert_idx, expert_weight, mark, peer, capacity, after_dispatch) -> torch.Tensor:
+        num_tokens, k = expert_idx.shape
         n, world, ops = num_tokens * k, self.world, self.ops
-        if self.capacity is None:
-            self.capacity = n
-        capacity = self.capacity
+        if capacity is None:
+            capacity = self.capacity = n
 
         # 1-2. Sort local copies by global expert (no padding), plan the slots.
         counts, offsets, sorted_token, copy_pos = ops.sort_copies(expert_idx, self.num_experts)
         send_index, return_row = ops.plan(offsets, sorted_token, copy_pos, world, self.experts_local, capacity,
                                           self.status)
         mark("dispatch plan")
-        if self.peer is not None:
+        if peer is not None:
             return self._forward_peer(x, expert_weight, counts, send_index, return_row, mark,
-                                      (counts, offsets, sorted_token, copy_pos))
+                                      (counts, offsets, sorted_token, copy_pos), peer, capacity, after_dispatch)
         # 3. Pack and exchange rows and counts.
         send = ops.gather_rows(x, send_index)  # [N*C, D]; rows of empty slots are never read
         recv_counts = self._all_to_all(counts.view(world, self.experts_local))
@@ -260,12 +316,15 @@ class ExpertParallelMoE:
         self.last = StepTrace((counts, offsets, sorted_token, copy_pos), send_index, return_row, recv_counts, slot_expert, topo)
         return out
 
-    def _forward_peer(self, x, expert_weight, counts, send_index, return_row, mark, source_sort) -> torch.Tensor:
+    def _forward_peer(self, x, expert_weight, counts, send_index, return_row, mark, source_sort, peer, capacity,
+                      after_dispatch) -> torch.Tensor:
         """Steps 3-5 with the rows stored directly into their owners' memory."""
-        ops, peer, capacity = self.ops, self.peer, self.capacity
+        ops = self.ops
         ops.push_counts(counts, peer.peer_counts, self.rank, self.experts_local)
         ops.push_rows(x, send_index, peer.peer_recv, self.rank, capacity)
         ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)
+        if after_dispatch is not None:
+            after_dispatch()
         mark("dispatch all-to-all")
         slot_expert = ops.slot_experts(peer.counts, capacity)
         topo = ops.route(slot_expert.view(-1, 1), self.experts_local, self.ffn_dim, BLOCK_SIZE)

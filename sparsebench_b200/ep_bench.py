@@ -23,6 +23,11 @@ from sparsebench_b200.workloads import CONFIGS, make_layer
 
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool; 900 nominal
 
+# Micro-batches per step by rank count, where measured to pay (the owner's matmuls tensor-bound and the
+# exchange a large share of the step); elsewhere the step runs whole.
+DEFAULT_MICRO_BATCHES: dict[int, int] = {}
+
+
 
 def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int) -> float:
     """Mean ms per step, max over ranks."""
@@ -91,13 +96,16 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     factor = getattr(args, "ep_capacity_factor", 3.0)
     capacity = min(n_copies, int(math.ceil(factor * n_copies / world / 128.0)) * 128)
     exchange = getattr(args, "ep_exchange", "peer") if world > 1 else "nccl"
+    # Micro-batches pipelined over streams (peer exchange): 0 = this build's default for the rank count.
+    micro_batches = getattr(args, "ep_micro_batches", 0) or DEFAULT_MICRO_BATCHES.get(world, 1)
     moe = None
     if exchange == "peer":
         # Rows stored straight into the owner's memory: only real rows travel, so the capacity can be
         # the exact worst case. If the buffers cannot be mapped on this machine every rank falls back.
         try:
             moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
-                                    fuse_return=not getattr(args, "ep_unfused_return", False))
+                                    fuse_return=not getattr(args, "ep_unfused_return", False),
+                                    micro_batches=micro_batches)
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line
             mapped = torch.zeros(1, device=device)
@@ -147,6 +155,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     route_launches = 1 if world * moe.capacity <= 262144 else 3
     fused_return = moe.peer is not None and moe.fuse_return
     launches_per_step = (12 if moe.peer is not None else 8) + route_launches - (1 if fused_return else 0)
+    if moe.micro_batches > 1:
+        launches_per_step = launches_per_step * moe.micro_batches + 1  # every part is a whole step, plus the concatenation
     with clock_sampler_cls(local) as clocks:
         ms_per_step = _timed_steps(step, flush, args.warmup, args.steps, world)
     value = world * cfg.useful_flops / (ms_per_step * 1e-3) / 1e12
@@ -167,6 +177,12 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     d2h = host_out.numel() * host_out.element_size()
 
     # ---- per-stage times on this rank (eager, an event at every stage mark) ---------------------------
+    # With micro-batches the stages of the parts interleave; the breakdown (and the roofline of the
+    # dominant matmul) is then taken on the same step run whole.
+    timed_moe = moe
+    if moe.micro_batches > 1:
+        moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
+                                fuse_return=timed_moe.fuse_return)
     names: list[str] = []
     sums: dict[str, float] = {}
     iters = max(5, min(args.steps, 30))
@@ -227,6 +243,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                    "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
                    "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
                    "exchange": exchange, "return_leg": "stored by the DSD epilogue" if fused_return else "separate kernel",
+                   "micro_batches": timed_moe.micro_batches,
                    "launch": launch, "l2": "256 MiB written before every step",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
         "clocks": clocks.summary(),

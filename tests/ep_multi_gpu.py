@@ -1,10 +1,11 @@
 """Expert-parallel parity on 2, 4 or 8 GPUs. Not collected by pytest; run it with torchrun:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29511 tests/ep_multi_gpu.py [nccl|peer|peer_unfused]
+        --master-port 29511 tests/ep_multi_gpu.py [nccl|peer|peer_unfused|peer_mb2|peer_mb4]
 
 (peer: the owner's DSD stores its rows into the source ranks' buffers from its epilogue;
-peer_unfused: DSD writes y and a second kernel pushes it.)
+peer_unfused: DSD writes y and a second kernel pushes it; peer_mbM: the step cut into M micro-batches
+pipelined over M streams.)
 
 Every rank builds the same global batch from a seed, keeps its T tokens and its E/N experts, runs
 one expert-parallel step eagerly and one through a CUDA graph with fresh tokens and routing, and
@@ -42,32 +43,7 @@ def global_batch(world: int, seed: int, case: str):
     return x, idx, gate
 
 
-def main() -> None:
-    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    g = torch.Generator().manual_seed(0)
-    w1 = (torch.randn(E, D, F, generator=g) / D**0.5).bfloat16()
-    w2 = (torch.randn(E, F, D, generator=g) / F**0.5).bfloat16()
-    mode = sys.argv[1] if len(sys.argv) > 1 else "nccl"
-    exchange = "peer" if mode.startswith("peer") else mode
-    layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
-                              capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused")
-    mine = slice(rank * T, (rank + 1) * T)
-
-    def check(out: torch.Tensor, x, idx, gate, what: str) -> None:
-        expected = M.moe_reference(x.float(), idx, gate.float(), w1.float(), w2.float())[mine]
-        torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2, msg=lambda m: f"{what}: {m}")
-
-    # Eager step.
-    x, idx, gate = global_batch(world, 1, "zipf")
-    dx, didx, dgate = x[mine].cuda(), idx[mine].cuda(), gate[mine].cuda()
-    out = layer(dx, didx, dgate)
-    torch.cuda.synchronize()
-    layer.check()
-    check(out, x, idx, gate, "eager")
-
-    # Layout: the exchange keeps the stable global copy order (global token = rank*T + t).
+def check_layout(layer, rank: int, world: int, idx: torch.Tensor) -> None:
     trace = layer.last
     global_token = torch.where(trace.send_index >= 0, trace.send_index + rank * T, -1).to(torch.int32)
     received = torch.empty_like(global_token)
@@ -84,6 +60,37 @@ def main() -> None:
         got = recv_np[rows[offs[e_local] : offs[e_local] + count]]
         start = int(whole.padded_offsets[e])
         assert np.array_equal(got, whole.row_token[start : start + count]), f"expert {e}: copy order differs"
+
+
+def main() -> None:
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    g = torch.Generator().manual_seed(0)
+    w1 = (torch.randn(E, D, F, generator=g) / D**0.5).bfloat16()
+    w2 = (torch.randn(E, F, D, generator=g) / F**0.5).bfloat16()
+    mode = sys.argv[1] if len(sys.argv) > 1 else "nccl"
+    exchange = "peer" if mode.startswith("peer") else mode
+    layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
+                              capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused",
+                              micro_batches=int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1)
+    mine = slice(rank * T, (rank + 1) * T)
+
+    def check(out: torch.Tensor, x, idx, gate, what: str) -> None:
+        expected = M.moe_reference(x.float(), idx, gate.float(), w1.float(), w2.float())[mine]
+        torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2, msg=lambda m: f"{what}: {m}")
+
+    # Eager step.
+    x, idx, gate = global_batch(world, 1, "zipf")
+    dx, didx, dgate = x[mine].cuda(), idx[mine].cuda(), gate[mine].cuda()
+    out = layer(dx, didx, dgate)
+    torch.cuda.synchronize()
+    layer.check()
+    check(out, x, idx, gate, "eager")
+
+    # Layout: the exchange keeps the stable global copy order (global token = rank*T + t).
+    if layer.micro_batches == 1:  # with micro-batches each part has its own layout; the outputs cover those
+        check_layout(layer, rank, world, idx)
 
     # Graph: capture once, replay with new tokens and routing.
     graph_ok = True
