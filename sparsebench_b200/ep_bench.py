@@ -25,7 +25,9 @@ NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool; 900 nominal
 
 # Micro-batches per step by rank count, where measured to pay (the owner's matmuls tensor-bound and the
 # exchange a large share of the step); elsewhere the step runs whole.
-DEFAULT_MICRO_BATCHES: dict[int, int] = {}
+# 8 ranks (16 experts each, the busiest rank tensor-bound): 0.469 ms whole, 0.427 ms in two parts; 2 ranks (64
+# experts each, HBM-bound): 0.335 ms whole, 0.465 ms in two parts.
+DEFAULT_MICRO_BATCHES: dict[int, int] = {8: 2}
 
 
 
