@@ -24,6 +24,10 @@
 //   A: 128 rows x 128 B; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)      (16 KB)
 //   B: kTileN/64 slabs of [64 k rows x 128 B], same swizzle                          (kTileN*128 B)
 //
+// Options (GemmParams): skip_padding leaves out the stores (both ops) and loads (DSD) of 32-row groups
+// that hold only padding; raster_rows walks the tiles in bands of row blocks for L2 reuse of the
+// weights; peer_out makes the DSD epilogue store each row into another rank's buffer instead of y.
+//
 // Every wait is bounded; on expiry the role records a bit in *dev_status, raises the CTA's abort
 // flag and all roles fall through to the common exit, where TMEM is released.
 #pragma once

@@ -14,7 +14,10 @@ slices of w1/w2 never move) and T local tokens. One step on a rank:
      a smaller C trades traffic for an overflow flag);
   4. the owner derives the local expert of every receive slot from the counts, runs routing
      (k = 1, empty slots skipped), SDD and DSD on the received rows exactly as on one GPU;
-  5. pack each slot's result row, exchange back, and combine with the local gates.
+  5. pack each slot's result row, exchange back, and combine with the local gates. With the peer
+     exchange the owner's DSD stores each result row into its source rank's buffer straight from
+     its epilogue (no y, no second kernel), and the step can be cut into micro-batches that overlap
+     one part's exchange with another part's matmuls.
 
 Slots arrive ordered by (source rank, expert, copy index), and the owner's sort is stable, so
 within an expert rows follow (source rank, copy index): the global copy order with global token
