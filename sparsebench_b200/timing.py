@@ -39,11 +39,15 @@ def time_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: int = 
     return statistics.median(time_each_ms(fn, flush, warmup, iters))
 
 
-def captured(fn: Callable[[], object]) -> tuple[torch.cuda.CUDAGraph, object]:
-    """fn() captured into a CUDA graph (after one eager call on a side stream, so that one-time
-    set-up stays outside the capture). Returns (graph, fn's result): keep the result alive as long as
-    the graph is replayed. Replaying puts the kernels on the GPU with no host work in between, so
-    events around graph.replay() time the kernels and not the Python and driver calls that launch them."""
+def kernel_time_ms(fn: Callable[[], object], flush: torch.Tensor | None, reps: int = 8, warmup: int = 3,
+                   iters: int = 20) -> float:
+    """Mean GPU time in ms of ONE call of fn(), measured as `reps` back-to-back calls captured in one
+    CUDA graph: events around a replay see `reps` launches with no host work between them, and the
+    one-off latency of launching the graph is spread over them. L2 is flushed before every replay;
+    between the launches inside a replay nothing is flushed, so this is for kernels whose inputs exceed
+    L2 anyway (here: 537 MB of expert weights per launch against 126 MB of L2). An eager launch timed
+    alone adds the host's launch work to a ~100 us kernel, and a timing event recorded inside a graph
+    adds a drain-and-restart bubble of several us per event; both were measured and rejected."""
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -51,5 +55,36 @@ def captured(fn: Callable[[], object]) -> tuple[torch.cuda.CUDAGraph, object]:
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        result = fn()
-    return graph, result
+        keep = [fn() for _ in range(reps)]
+    samples = time_each_ms(graph.replay, flush, warmup, iters)
+    del graph, keep
+    return statistics.mean(samples) / reps
+
+
+def marginal_stage_times_ms(stages: list[tuple[str, Callable[[dict], None]]], flush: torch.Tensor | None,
+                            warmup: int = 3, iters: int = 20) -> dict[str, float]:
+    """GPU time in ms of every stage of a pipeline IN ITS PLACE in the pipeline: the graph of the first
+    j stages is timed for j = 1..n (CUDA events around each replay, L2 flushed before it), and stage j
+    gets the difference between prefix j and prefix j-1. The one-off latency of launching a graph is
+    the same in every prefix and cancels, each stage runs after its real predecessor with the cache
+    state that predecessor leaves, and nothing is inserted between the kernels. The first stage keeps
+    the graph-launch latency. Each stage is a callable that reads and writes a shared dict."""
+    means: list[float] = []
+    for j in range(1, len(stages) + 1):
+        def run(j: int = j) -> dict:
+            state: dict = {}
+            for _, stage in stages[:j]:
+                stage(state)
+            return state
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            run()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = run()
+        means.append(statistics.mean(time_each_ms(graph.replay, flush, warmup, iters)))
+        del graph, keep
+    return {name: means[j] - (means[j - 1] if j else 0.0) for j, (name, _) in enumerate(stages)}
