@@ -1,8 +1,8 @@
 """The expert-parallel arm of bench.py: one rank per GPU under torchrun (or a single process for
 world size 1). Weak scaling: every rank brings T tokens, the E experts are split over the ranks.
 
-Timing: CUDA events around every step on the launching stream, 256 MiB written before every step
-to flush L2, a barrier and a device synchronise on both sides of the timed region, per-rank sums
+Timing: CUDA events around every step on the launching stream, 256 MiB written and read back before
+every step to flush L2, a barrier and a device synchronise on both sides of the timed region, per-rank sums
 reduced with MAX. The step is one CUDA-graph replay when the collectives can be captured, else
 eager launches (config.launch says which).
 """
@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from sparsebench_b200.ep import ExpertParallelMoE
-from sparsebench_b200.timing import l2_flush_buffer
+from sparsebench_b200.timing import flush_l2, l2_flush_buffer
 from sparsebench_b200.workloads import CONFIGS, make_layer
 
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool; 900 nominal
@@ -41,7 +41,7 @@ def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int)
     torch.cuda.synchronize()
     pairs = []
     for _ in range(steps):
-        flush.zero_()
+        flush_l2(flush)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         step()
@@ -189,7 +189,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     sums: dict[str, float] = {}
     iters = max(5, min(args.steps, 30))
     for it in range(iters + 2):
-        flush.zero_()
+        flush_l2(flush)
         events = [torch.cuda.Event(enable_timing=True)]
         events[0].record()
         seen: list[str] = []
@@ -246,7 +246,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                    "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
                    "exchange": exchange, "return_leg": "stored by the DSD epilogue" if fused_return else "separate kernel",
                    "micro_batches": timed_moe.micro_batches,
-                   "launch": launch, "l2": "256 MiB written before every step",
+                   "launch": launch, "l2": "256 MiB written and read back before every step (L2 cold and clean)",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
         "clocks": clocks.summary(),
         "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,

@@ -16,15 +16,30 @@ def l2_flush_buffer(device: torch.device | str = "cuda") -> torch.Tensor:
     return torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
 
 
-def time_each_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: int = 3, iters: int = 20) -> list[float]:
+def flush_l2(buffer: torch.Tensor) -> None:
+    """Empties L2 of everything the timed code could hit: writes the whole buffer (twice the size of L2),
+    then reads it back once. The write alone would leave L2 full of DIRTY lines, and the first ~20 us
+    of whatever is timed next would pay for writing 126 MB of them back to HBM; after the read pass L2
+    holds clean lines of the buffer only. Enqueued on the current stream; no sync."""
+    buffer.zero_()
+    torch.sum(buffer.view(torch.int64))
+
+
+def time_each_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: int = 3, iters: int = 20,
+                 leave_l2_dirty: bool = False) -> list[float]:
     """GPU time of every one of `iters` calls of fn(), in ms. Events are recorded on torch's
-    current stream, which is the stream the kernels are launched on."""
+    current stream, which is the stream the kernels are launched on. leave_l2_dirty: flush by the
+    write pass alone (the reference's way), so that fn() also pays for the write-back of an L2 full of
+    dirty lines."""
     for _ in range(warmup):
         fn()
     samples = []
     for _ in range(iters):
         if flush is not None:
-            flush.zero_()
+            if leave_l2_dirty:
+                flush.zero_()
+            else:
+                flush_l2(flush)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()
