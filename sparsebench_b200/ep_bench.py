@@ -40,8 +40,13 @@ def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int)
         dist.barrier()
     torch.cuda.synchronize()
     pairs = []
+    aligned = torch.zeros(1, device=flush.device)
     for _ in range(steps):
         flush_l2(flush)
+        if world > 1:
+            # The ranks' flushes do not take exactly the same time; without this the rank that finishes
+            # first would spend the difference waiting inside its timed step, at the first exchange.
+            dist.all_reduce(aligned)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         step()
