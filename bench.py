@@ -126,21 +126,33 @@ class ClockSampler:
 def pipelined_e2e_ms(forward, host_inputs, weights, warmup: int, steps: int) -> float:
     """ms per step of `forward` fed from pinned HOST buffers when consecutive steps overlap the way a
     serving loop runs them: step i+1's inputs are copied in while step i computes and step i-1's
-    result is copied out (three streams, two sets of device buffers). Every step's host->device and
-    device->host copies are inside the timed region; the weights (1 GB, far larger than L2) are
-    re-streamed from HBM by every step."""
+    result is copied out (three streams, two sets of device buffers, the layer of each set captured
+    once as a CUDA graph and replayed, so that the host only enqueues copies and one graph launch per
+    step). Every step's host->device and device->host copies are inside the timed region; the
+    weights (1 GB, far larger than L2) are re-streamed from HBM by every step."""
     host_x, host_idx, host_w = host_inputs
     device = weights[0].device
     copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
     sets = []
     for _ in range(2):
-        sets.append({
+        b = {
             "x": torch.empty(host_x.shape, dtype=host_x.dtype, device=device),
             "idx": torch.empty(host_idx.shape, dtype=host_idx.dtype, device=device),
             "w": torch.empty(host_w.shape, dtype=host_w.dtype, device=device),
             "out": torch.empty(host_x.shape, dtype=host_x.dtype).pin_memory(),
-            "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(),
-        })
+            "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "copied": torch.cuda.Event(),
+        }
+        b["x"].copy_(host_x)
+        b["idx"].copy_(host_idx)
+        b["w"].copy_(host_w)
+        torch.cuda.synchronize(device)
+        with torch.cuda.stream(compute):
+            forward(b["x"], b["idx"], b["w"], *weights)  # one-time set-up outside the capture
+        torch.cuda.synchronize(device)
+        b["graph"] = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(b["graph"], stream=compute):
+            b["result"] = forward(b["x"], b["idx"], b["w"], *weights)
+        sets.append(b)
 
     def run(n: int) -> None:
         for i in range(n):
@@ -153,12 +165,13 @@ def pipelined_e2e_ms(forward, host_inputs, weights, warmup: int, steps: int) -> 
                 b["loaded"].record(copy_in)
             with torch.cuda.stream(compute):
                 compute.wait_event(b["loaded"])
-                result = forward(b["x"], b["idx"], b["w"], *weights)
+                compute.wait_event(b["copied"])  # the graph's output buffer has been read out
+                b["graph"].replay()
                 b["computed"].record(compute)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(b["computed"])
-                result.record_stream(copy_out)
-                b["out"].copy_(result, non_blocking=True)
+                b["out"].copy_(b["result"], non_blocking=True)
+                b["copied"].record(copy_out)
 
     torch.cuda.synchronize(device)
     run(max(warmup, 4))
@@ -300,14 +313,13 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     # ---- e2e: public API, host buffers, copies inside the timed region -------------------------------
     host_x, host_idx, host_w = (t.pin_memory() for t in (layer.x, layer.expert_idx, layer.expert_weight))
     host_out = torch.empty_like(layer.x).pin_memory()
-    dx, didx, dw = torch.empty_like(dev.x), torch.empty_like(dev.expert_idx), torch.empty_like(dev.expert_weight)
-
     def e2e_step() -> None:
-        dx.copy_(host_x, non_blocking=True)
-        didx.copy_(host_idx, non_blocking=True)
-        dw.copy_(host_w, non_blocking=True)
-        result = moe_forward(dx, didx, dw, dev.w1, dev.w2)
-        host_out.copy_(result, non_blocking=True)
+        # The layer is the graph captured above; its inputs live in dev.x / dev.expert_idx / dev.expert_weight.
+        dev.x.copy_(host_x, non_blocking=True)
+        dev.expert_idx.copy_(host_idx, non_blocking=True)
+        dev.expert_weight.copy_(host_w, non_blocking=True)
+        graph.replay()
+        host_out.copy_(graph_out, non_blocking=True)
 
     e2e_ms = time_each_ms(e2e_step, flush, warmup=args.warmup, iters=args.steps)
     e2e_latency_ms = sum(e2e_ms) / len(e2e_ms)  # one step alone: copy in, layer, copy out, nothing overlapped
@@ -394,8 +406,8 @@ def run_single_gpu(args: argparse.Namespace) -> None:
         "clocks": clocks.summary(),
         "e2e": {"value": cfg.useful_flops / (e2e_ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms_per_step, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "how": "steps pipelined over three streams (copy in, layer, copy out), two buffer sets; every "
-                       "step's H2D and D2H copies are inside the timed region",
+                "how": "steps pipelined over three streams (copy in, layer as a CUDA-graph replay, copy out), two buffer "
+                       "sets; every step's H2D and D2H copies are inside the timed region",
                 "single_step_latency_ms": e2e_latency_ms},
         "gpu_launches": 4 * args.steps,
         "roofline": roofline,

