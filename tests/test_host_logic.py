@@ -88,3 +88,20 @@ def test_layer_config_flops_and_shapes() -> None:
     assert torch.equal(layer.x, again.x) and torch.equal(layer.w2, again.w2)
     other_tokens = workloads.make_layer(small, seed=1, token_seed=5)
     assert torch.equal(layer.w1, other_tokens.w1) and not torch.equal(layer.x, other_tokens.x)
+
+
+def test_expert_parallel_argument_errors() -> None:
+    # Without a process group the layer is a single rank: the peer exchange options have nothing to act on.
+    from sparsebench_b200.ep import ExpertParallelMoE
+
+    w1, w2 = torch.zeros(4, 64, 256, dtype=torch.bfloat16), torch.zeros(4, 256, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="micro_batches"):
+        ExpertParallelMoE(w1, w2, 4, micro_batches=2)
+    with pytest.raises(ValueError, match="micro_batches"):
+        ExpertParallelMoE(w1, w2, 4, micro_batches=0)
+    with pytest.raises(ValueError, match="exchange"):
+        ExpertParallelMoE(w1, w2, 4, exchange="mpi")
+    with pytest.raises(ValueError, match="do not split"):
+        ExpertParallelMoE(w1, w2, 8)
+    with pytest.raises(ValueError, match="w2_local"):
+        ExpertParallelMoE(w1, w2.transpose(1, 2), 4)
