@@ -270,7 +270,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
 def run_single_gpu(args: argparse.Namespace) -> None:
     from sparsebench_b200 import _C, moe_forward, route_device
     from sparsebench_b200.spmm import combine, dsd, sdd
-    from sparsebench_b200.timing import kernel_time_ms, l2_flush_buffer, marginal_stage_times_ms, time_each_ms
+    from sparsebench_b200.timing import l2_flush_buffer, marginal_stage_times_ms, time_each_ms
 
     cfg = CONFIGS[args.workload or "fine_grained"]
     torch.cuda.set_device(0)
@@ -336,8 +336,7 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     y = dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
     iters = max(5, min(args.steps, 50))
     # Each kernel's time in its place in the layer: differences between the graphs of the first j stages
-    # (see marginal_stage_times_ms); routing, the first stage, is timed as back-to-back launches instead
-    # so that it does not carry the graph-launch latency.
+    # (see marginal_stage_times_ms).
     def stage_route(state: dict) -> None:
         state["topo"] = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
 
@@ -352,15 +351,9 @@ def run_single_gpu(args: argparse.Namespace) -> None:
 
     stage_ms = marginal_stage_times_ms([("routing", stage_route), ("sdd", stage_sdd), ("dsd", stage_dsd),
                                         ("combine", stage_combine)], flush, 3, iters)
-    # The two small kernels sit at the ends of the graph, where the difference also carries the graph's
-    # launch latency (routing) and the change in how the graph drains (combine: 1 us measured that way):
-    # they are timed as back-to-back launches instead.
-    stage_ms["routing"] = kernel_time_ms(lambda: route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128), flush, 8,
-                                         3, iters)
-    stage_ms["combine"] = kernel_time_ms(lambda: combine(y, dev.expert_weight, topo), flush, 8, 3, iters)
-    stage_timing = ("sdd, dsd: each in its place in the layer, CUDA-graph replays of the first j stages with CUDA events "
-                    "around every replay and L2 flushed before it, stage j = prefix j - prefix j-1; routing, combine: "
-                    "8 back-to-back launches in one graph")
+    stage_timing = ("each kernel in its place in the layer: CUDA-graph replays of the first j stages (each closed by the "
+                    "same one-element kernel), CUDA events around every replay, L2 flushed before it, stage j = "
+                    "prefix j - prefix j-1")
     rows = live_rows(layer.expert_idx, cfg.num_experts)            # executed by the tensor cores
     rows_moved = live_rows(layer.expert_idx, cfg.num_experts, 32)  # stored / loaded
     n_copies = cfg.num_tokens * cfg.k

@@ -79,17 +79,21 @@ def kernel_time_ms(fn: Callable[[], object], flush: torch.Tensor | None, reps: i
 def marginal_stage_times_ms(stages: list[tuple[str, Callable[[dict], None]]], flush: torch.Tensor | None,
                             warmup: int = 3, iters: int = 20) -> dict[str, float]:
     """GPU time in ms of every stage of a pipeline IN ITS PLACE in the pipeline: the graph of the first
-    j stages is timed for j = 1..n (CUDA events around each replay, L2 flushed before it), and stage j
-    gets the difference between prefix j and prefix j-1. The one-off latency of launching a graph is
-    the same in every prefix and cancels, each stage runs after its real predecessor with the cache
-    state that predecessor leaves, and nothing is inserted between the kernels. The first stage keeps
-    the graph-launch latency. Each stage is a callable that reads and writes a shared dict."""
+    j stages is timed for j = 0..n (CUDA events around each replay, L2 flushed before it), and stage j
+    gets the difference between prefix j and prefix j-1. Every prefix ends with the same one-element
+    kernel, so that each graph ends the same way (a small kernel waiting for its predecessor to
+    finish) whatever its last stage is; prefix 0 is that kernel alone. The one-off latency of launching
+    a graph and the cost of the closing kernel are the same in every prefix and cancel, each stage runs
+    after its real predecessor with the cache state that predecessor leaves, and nothing is inserted
+    between the stages. Each stage is a callable that reads and writes a shared dict."""
+    closing = torch.zeros(1, device="cuda")
     means: list[float] = []
-    for j in range(1, len(stages) + 1):
+    for j in range(len(stages) + 1):
         def run(j: int = j) -> dict:
             state: dict = {}
             for _, stage in stages[:j]:
                 stage(state)
+            closing.add_(1.0)
             return state
 
         side = torch.cuda.Stream()
@@ -102,4 +106,4 @@ def marginal_stage_times_ms(stages: list[tuple[str, Callable[[dict], None]]], fl
             keep = run()
         means.append(statistics.mean(time_each_ms(graph.replay, flush, warmup, iters)))
         del graph, keep
-    return {name: means[j] - (means[j - 1] if j else 0.0) for j, (name, _) in enumerate(stages)}
+    return {name: means[j + 1] - means[j] for j, (name, _) in enumerate(stages)}
