@@ -54,28 +54,6 @@ def time_ms(fn: Callable[[], object], flush: torch.Tensor | None, warmup: int = 
     return statistics.median(time_each_ms(fn, flush, warmup, iters))
 
 
-def kernel_time_ms(fn: Callable[[], object], flush: torch.Tensor | None, reps: int = 8, warmup: int = 3,
-                   iters: int = 20) -> float:
-    """Mean GPU time in ms of ONE call of fn(), measured as `reps` back-to-back calls captured in one
-    CUDA graph: events around a replay see `reps` launches with no host work between them, and the
-    one-off latency of launching the graph is spread over them. L2 is flushed before every replay;
-    between the launches inside a replay nothing is flushed, so this is for kernels whose inputs exceed
-    L2 anyway (here: 537 MB of expert weights per launch against 126 MB of L2). An eager launch timed
-    alone adds the host's launch work to a ~100 us kernel, and a timing event recorded inside a graph
-    adds a drain-and-restart bubble of several us per event; both were measured and rejected."""
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        fn()
-    torch.cuda.current_stream().wait_stream(side)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        keep = [fn() for _ in range(reps)]
-    samples = time_each_ms(graph.replay, flush, warmup, iters)
-    del graph, keep
-    return statistics.mean(samples) / reps
-
-
 def marginal_stage_times_ms(stages: list[tuple[str, Callable[[dict], None]]], flush: torch.Tensor | None,
                             warmup: int = 3, iters: int = 20) -> dict[str, float]:
     """GPU time in ms of every stage of a pipeline IN ITS PLACE in the pipeline: the graph of the first
