@@ -412,12 +412,24 @@ def run_single_gpu(args: argparse.Namespace) -> None:
         # what their per-GPU throughput should be compared with, so it rides along on this line.
         del dev, layer, graph, graph_out, out, h, y, topo
         torch.cuda.empty_cache()
-        from sparsebench_b200 import ep_bench
-
-        short = argparse.Namespace(**{**vars(args), "workload": "expert_parallel", "steps": min(args.steps, 50)})
-        ep_line = ep_bench.measure(short, METRIC, measured_peaks(), ClockSampler, 1, 0, 0)
-        line["expert_parallel_1gpu"] = {k: ep_line[k] for k in ("value", "unit", "ms_per_step", "steps")}
-        line["expert_parallel_1gpu"]["workload"] = ep_line["config"]["workload"]
+        ep_cfg = CONFIGS["expert_parallel"]
+        ep_dev = make_layer(ep_cfg, seed=0).to(device)
+        ep_args = (ep_dev.x, ep_dev.expert_idx, ep_dev.expert_weight, ep_dev.w1, ep_dev.w2)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            moe_forward(*ep_args)
+        torch.cuda.current_stream().wait_stream(side)
+        ep_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ep_graph):
+            ep_out = moe_forward(*ep_args)
+        ep_steps = min(args.steps, 50)
+        ep_ms = statistics.mean(time_each_ms(ep_graph.replay, flush, warmup=args.warmup, iters=ep_steps))
+        line["expert_parallel_1gpu"] = {
+            "value": ep_cfg.useful_flops / (ep_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ep_ms, "steps": ep_steps,
+            "workload": ep_cfg.name, "how": "the plain layer (all 128 experts on this GPU, no exchange), one graph replay per step",
+        }
+        del ep_graph, ep_out, ep_dev, ep_args
     print(json.dumps(line))
 
 
