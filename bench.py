@@ -19,10 +19,14 @@ Prints ONE JSON line (rank 0):
              back, all inside the timed region; consecutive steps overlap on three streams the way
              a serving loop runs them (the unoverlapped single-step latency is reported beside it)
   roofline   the dominant kernel's algorithmic bytes / its measured duration against the measured
-             HBM copy bandwidth of this pool (MEASURED_PEAKS.json, else the stated fallback)
-  cpu_baseline  the fp32 CPU oracle of the same layer timed on this machine's host cores
+             HBM copy bandwidth (MEASURED_PEAKS.json next to this file, else the stated fallback)
+  cpu_baseline  the reference's fp32 CPU implementation of the same layer timed on this machine's
+             host cores; its output doubles as the parity check of the GPU result (`parity`)
+  other_workloads / expert_parallel_1gpu / library_baselines   the other single-GPU configurations,
+             the one-GPU value of the multi-GPU workload, and stock-PyTorch pipelines of the same layer
 
---impl reference times only that CPU implementation and prints its own line.
+`config` names the workload only and is identical in both arms; `method` says how it was run.
+--impl reference times only the CPU implementation and prints its own line.
 """
 
 from __future__ import annotations
@@ -45,11 +49,34 @@ if str(ROOT) not in sys.path:
 from sparsebench_b200.workloads import CONFIGS, LayerConfig, make_layer  # noqa: E402
 
 METRIC = "moe_fwd_useful_tflops"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
-# profiles/bsr_gemm_kernel_fine_grained.md (same workload, same kernels).
-NCU_TRAFFIC_BYTES = {("fine_grained", "sdd"): 576.8e6, ("fine_grained", "dsd"): 619.1e6}
-FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+# Used only if MEASURED_PEAKS.json is absent: an earlier copy-bandwidth / cuBLAS bf16 measurement on B200.
+FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from profiler captures: a tracked
+# table keyed by workload and kernel, each entry with the fingerprint of the kernel sources it was taken on.
+TRAFFIC_TABLE = ROOT / "profiles" / "dram_traffic.json"
+KERNEL_SOURCES = ["bsr_gemm.cuh", "ptx_sm100.cuh", "sdd.cu", "dsd.cu"]
+
+
+def kernel_source_fingerprint() -> str:
+    import hashlib
+
+    digest = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        digest.update((ROOT / "sparsebench_b200" / "csrc" / name).read_bytes())
+    return digest.hexdigest()[:16]
+
+
+def profiled_traffic(workload: str, kernel: str) -> tuple[float | None, str]:
+    """(bytes per launch or None, where it comes from / why it is missing)."""
+    if not TRAFFIC_TABLE.exists():
+        return None, "no profiler capture table"
+    for entry in json.loads(TRAFFIC_TABLE.read_text()).get("entries", []):
+        if entry.get("workload") == workload and entry.get("kernel") == kernel:
+            if entry.get("kernel_sources_sha16") != kernel_source_fingerprint():
+                return None, f"stale: captured at {entry.get('commit')} on other kernel sources ({entry.get('summary')})"
+            return float(entry["dram_bytes_per_launch"]), f"profiler capture at {entry.get('commit')}: {entry.get('summary')}"
+    return None, "no profiler capture of this kernel on this workload"
 
 
 def measured_peaks() -> tuple[float, float, str]:
@@ -186,6 +213,124 @@ def pipelined_e2e_ms(forward, host_inputs, weights, warmup: int, steps: int) -> 
     return start.elapsed_time(end) / steps
 
 
+def workload_config(cfg: LayerConfig) -> dict:
+    """The `config` object of the JSON line: the workload only, identical in both arms."""
+    return {"workload": cfg.name, "tokens": cfg.num_tokens, "d_model": cfg.d_model, "ffn_dim": cfg.ffn_dim,
+            "experts": cfg.num_experts, "top_k": cfg.k, "routing": cfg.routing, "block_size": 128}
+
+
+def reference_cpu_layer():
+    """(moe_reference, kind): the reference's own CPU implementation (its sparsebench/reference.py, loaded
+    unmodified from the copy under baseline/_ref through the `sparsebench` import name) when that copy is
+    present, kind "reference"; otherwise the oracle's restatement of it, kind "port"."""
+    try:
+        import sparsebench
+
+        if sparsebench.reference_py_dir() is not None:
+            from sparsebench.reference import moe_reference
+
+            return moe_reference, "reference"
+    except Exception:  # noqa: BLE001 - fall through to the port
+        pass
+    from oracle import moe as oracle_moe
+
+    return oracle_moe.moe_reference, "port"
+
+
+def cpu_baseline(cfg: LayerConfig, layer, gpu_out: torch.Tensor | None, budget_s: float = 20.0) -> tuple[dict, dict]:
+    """The reference's fp32 CPU layer on this machine's host cores: (cpu_baseline, parity). Its output is
+    also the check of the GPU result: every row of `gpu_out` against it, rtol = atol = 2e-2."""
+    moe_reference, kind = reference_cpu_layer()
+    x, w = layer.x.float(), layer.expert_weight.float()
+    w1, w2 = layer.w1.float(), layer.w2.float()
+    times = []
+    started = time.perf_counter()
+    expected = None
+    for i in range(7):
+        t0 = time.perf_counter()
+        expected = moe_reference(x, layer.expert_idx, w, w1, w2)
+        dt = time.perf_counter() - t0
+        if i >= 2:
+            times.append(dt)
+        if time.perf_counter() - started > budget_s and len(times) >= 1:
+            break
+    med = statistics.median(times)
+    baseline = {
+        "value": cfg.useful_flops / med / 1e12,
+        "unit": "TFLOP/s",
+        "ms_per_step": med * 1e3,
+        "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(),
+        "kind": kind,
+        "sample": f"whole {cfg.name} layer in fp32, median of {len(times)} runs after 2 warm-up runs",
+    }
+    parity = {"ok": None, "reason": "no GPU output given"}
+    if gpu_out is not None:
+        got = gpu_out.float().cpu()
+        err = (got - expected).abs()
+        parity = {"rows_checked": int(got.shape[0]), "max_abs_err": float(err.max()),
+                  "ok": bool((err <= 2e-2 + 2e-2 * expected.abs()).all()),
+                  "against": f"the reference's fp32 CPU layer ({kind}) on the same bf16 inputs, rtol = atol = 2e-2"}
+    return baseline, parity
+
+
+def run_reference_arm(args: argparse.Namespace) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = CONFIGS[args.workload or ("fine_grained" if args.gpus == 1 else "expert_parallel")]
+    if args.gpus > 1:
+        import bench_ep
+
+        config = bench_ep.workload_config(cfg, args.gpus)
+        # the CPU arm computes (a sample of) the global batch of all ranks' tokens
+        cfg = LayerConfig(cfg.name, cfg.num_tokens * args.gpus, cfg.d_model, cfg.ffn_dim, cfg.num_experts, cfg.routing)
+    else:
+        config = workload_config(cfg)
+    moe_reference, kind = reference_cpu_layer()
+
+    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm is alone on the host, so it takes
+    # every core the process may run on.
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+    layer = make_layer(cfg, seed=0)
+    x, w = layer.x.float(), layer.expert_weight.float()
+    w1, w2 = layer.w1.float(), layer.w2.float()
+    # A step here is a bounded sample: the first `sample_tokens` tokens of the batch through the whole
+    # layer, halved until steps + warmup fit in about four minutes on the host cores.
+    sample_tokens = min(cfg.num_tokens, 4096)
+    steps, warmup = args.steps, args.warmup
+    while True:
+        xs, idx, ws = x[:sample_tokens], layer.expert_idx[:sample_tokens], w[:sample_tokens]
+        t0 = time.perf_counter()
+        moe_reference(xs, idx, ws, w1, w2)
+        if (time.perf_counter() - t0) * (steps + warmup) <= 240.0 or sample_tokens <= 64:
+            break
+        sample_tokens //= 2
+    for _ in range(max(0, warmup - 1)):
+        moe_reference(xs, idx, ws, w1, w2)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        moe_reference(xs, idx, ws, w1, w2)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    flops = 4 * sample_tokens * cfg.k * cfg.d_model * cfg.ffn_dim
+    value = flops / sec / 1e12
+    sample = (f"{sample_tokens} of {cfg.num_tokens} tokens through the whole fp32 layer per step, median of {steps} "
+              f"steps after {warmup} warm-up steps")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config,
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
 def live_rows(expert_idx: torch.Tensor, num_experts: int, granule: int = 128) -> int:
     """Rows of the layout after rounding every expert's copies up to `granule`: 128 is what the tensor
     cores execute (whole row blocks), 32 what SDD stores and DSD loads and stores in the layer (groups
@@ -194,83 +339,140 @@ def live_rows(expert_idx: torch.Tensor, num_experts: int, granule: int = 128) ->
     return int(((counts + granule - 1) // granule * granule).sum())
 
 
-def cpu_baseline(cfg: LayerConfig, layer, budget_s: float = 20.0) -> dict:
-    """The fp32 CPU oracle (a port of the reference's moe_reference) on this machine's host cores."""
-    from oracle import moe as oracle_moe
+def capture_layer(dev):
+    """(graph, graph_out, eager_out) of moe_forward over the fixed device tensors of `dev`."""
+    from sparsebench_b200 import moe_forward
 
-    x, w = layer.x.float(), layer.expert_weight.float()
-    w1, w2 = layer.w1.float(), layer.w2.float()
-    times = []
-    started = time.perf_counter()
-    for i in range(7):
-        t0 = time.perf_counter()
-        oracle_moe.moe_reference(x, layer.expert_idx, w, w1, w2)
-        dt = time.perf_counter() - t0
-        if i >= 2:
-            times.append(dt)
-        if time.perf_counter() - started > budget_s and len(times) >= 1:
-            break
-    med = statistics.median(times)
-    return {
-        "value": cfg.useful_flops / med / 1e12,
-        "unit": "TFLOP/s",
-        "ms_per_step": med * 1e3,
-        "cores": torch.get_num_threads(),
-        "host_cpus": os.cpu_count(),
-        "kind": "port",
-        "sample": f"whole {cfg.name} layer in fp32, median of {len(times)} runs after 2 warm-up runs",
+    args = (dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
+    out = moe_forward(*args)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        moe_forward(*args)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        graph_out = moe_forward(*args)
+    torch.cuda.synchronize()
+    return graph, graph_out, out
+
+
+def require_clean_status(device: torch.device, when: str) -> None:
+    from sparsebench_b200 import _C
+
+    status = int(_C.device_status(device).item())
+    if status != 0:
+        raise SystemExit(f"{when}: device status word is {status}: a bounded device-side wait of a matmul kernel expired")
+
+
+def stage_roofline(cfg: LayerConfig, layer, dev, flush, iters: int, peaks: tuple[float, float, str]) -> dict:
+    """Each kernel's time in its place in the layer and the roofline of the slower matmul."""
+    from sparsebench_b200 import route_device
+    from sparsebench_b200.spmm import combine, dsd, sdd
+    from sparsebench_b200.timing import marginal_stage_times_ms
+
+    hbm_gbs, bf16_tflops, peak_kind = peaks
+    w2_cat = dev.w2.view(cfg.num_experts * cfg.ffn_dim, cfg.d_model)
+
+    def stage_route(state: dict) -> None:
+        state["topo"] = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
+
+    def stage_sdd(state: dict) -> None:
+        state["h"] = sdd(dev.x, dev.w1, state["topo"], skip_padding_rows=True)
+
+    def stage_dsd(state: dict) -> None:
+        state["y"] = dsd(state["h"], w2_cat, state["topo"], version=5, skip_padding_rows=True)
+
+    def stage_combine(state: dict) -> None:
+        state["out"] = combine(state["y"], dev.expert_weight, state["topo"])
+
+    stage_ms = marginal_stage_times_ms([("routing", stage_route), ("sdd", stage_sdd), ("dsd", stage_dsd),
+                                        ("combine", stage_combine)], flush, 3, iters)
+    rows = live_rows(layer.expert_idx, cfg.num_experts)            # executed by the tensor cores
+    rows_moved = live_rows(layer.expert_idx, cfg.num_experts, 32)  # stored / loaded
+    n_copies = cfg.num_tokens * cfg.k
+    weight_bytes = cfg.num_experts * cfg.d_model * cfg.ffn_dim * 2
+    stage_bytes = {
+        "sdd": cfg.num_tokens * cfg.d_model * 2 + weight_bytes + rows_moved * cfg.ffn_dim * 2,
+        "dsd": rows_moved * cfg.ffn_dim * 2 + weight_bytes + rows_moved * cfg.d_model * 2,
+        "combine": n_copies * cfg.d_model * 2 + n_copies * 6 + cfg.num_tokens * cfg.d_model * 2,
     }
+    stage_flops = {"sdd": 2 * n_copies * cfg.d_model * cfg.ffn_dim, "dsd": 2 * n_copies * cfg.d_model * cfg.ffn_dim}
+    dominant = max(("sdd", "dsd"), key=lambda name: stage_ms[name])
+    t_dom = stage_ms[dominant] * 1e-3
+    hbm_time = stage_bytes[dominant] / (hbm_gbs * 1e9)
+    exec_flops = 2 * rows * cfg.d_model * cfg.ffn_dim  # one matmul, padding rows included
+    if hbm_time >= exec_flops / (bf16_tflops * 1e12):
+        achieved = stage_bytes[dominant] / t_dom / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs}
+    else:
+        achieved = exec_flops / t_dom / 1e12
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_tflops, "unit": "TFLOP/s",
+                    "frac": achieved / bf16_tflops}
+    traffic, traffic_source = profiled_traffic(cfg.name, dominant)
+    roofline.update({
+        "kernel": f"bsr_gemm_kernel<{dominant}>",
+        "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
+        "launch_ms": stage_ms[dominant], "algorithmic_bytes": stage_bytes[dominant], "live_rows": rows,
+        "rows_moved": rows_moved, "traffic": traffic, "traffic_source": traffic_source,
+        "stages_ms": stage_ms,
+        "stages_timing": "each kernel in its place in the layer: CUDA-graph replays of the first j stages (each closed by "
+                         "the same one-element kernel), CUDA events around every replay, L2 flushed before it, stage j = "
+                         "prefix j - prefix j-1",
+        "stages_frac_of_hbm_peak": {name: stage_bytes[name] / (stage_ms[name] * 1e-3) / 1e9 / hbm_gbs for name in stage_bytes},
+        "stages_executed_tflops": {name: exec_flops / (stage_ms[name] * 1e-3) / 1e12 for name in stage_flops},
+        "stages_useful_tflops": {name: stage_flops[name] / (stage_ms[name] * 1e-3) / 1e12 for name in stage_flops},
+    })
+    return roofline
 
 
-def run_reference_arm(args: argparse.Namespace) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    cfg = CONFIGS[args.workload or ("fine_grained" if args.gpus == 1 else "expert_parallel")]
-    if args.gpus > 1:  # the CPU arm computes the global batch of all ranks' tokens
-        cfg = LayerConfig(cfg.name, cfg.num_tokens * args.gpus, cfg.d_model, cfg.ffn_dim, cfg.num_experts, cfg.routing)
-    from oracle import moe as oracle_moe
+def measure_other_workload(name: str, args: argparse.Namespace, device: torch.device, flush: torch.Tensor,
+                           peaks: tuple[float, float, str], with_stages: bool = True) -> dict:
+    """One of the other single-GPU configurations, measured like the headline one (graph replays, L2 flushed,
+    clocks sampled during its own timed region), without the end-to-end and CPU legs."""
+    from sparsebench_b200.timing import time_each_ms
 
-    # torchrun pins OMP_NUM_THREADS to 1 for its workers; this arm is alone on the host, so it takes
-    # every core the process may run on.
-    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
+    cfg = CONFIGS[name]
     layer = make_layer(cfg, seed=0)
-    x, w = layer.x.float(), layer.expert_weight.float()
-    w1, w2 = layer.w1.float(), layer.w2.float()
-    # A step here is a bounded sample: the first `sample_tokens` tokens of the batch through the
-    # whole layer, so that steps + warmup stay within a few minutes on the host cores.
-    sample_tokens = min(cfg.num_tokens, 4096)
-    xs, idx, ws = x[:sample_tokens], layer.expert_idx[:sample_tokens], w[:sample_tokens]
-    steps, warmup = min(args.steps, 10), min(args.warmup, 2)
-    for _ in range(warmup):
-        oracle_moe.moe_reference(xs, idx, ws, w1, w2)
-    times = []
-    for _ in range(steps):
-        t0 = time.perf_counter()
-        oracle_moe.moe_reference(xs, idx, ws, w1, w2)
-        times.append(time.perf_counter() - t0)
-    sec = sum(times) / len(times)
-    flops = 4 * sample_tokens * cfg.k * cfg.d_model * cfg.ffn_dim
-    value = flops / sec / 1e12
-    sample = f"{sample_tokens} of {cfg.num_tokens} tokens through the whole fp32 layer per step, {steps} steps"
-    line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens": cfg.num_tokens, "d_model": cfg.d_model, "ffn_dim": cfg.ffn_dim,
-                   "experts": cfg.num_experts, "top_k": cfg.k, "routing": cfg.routing},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line))
+    dev = layer.to(device)
+    graph, graph_out, out = capture_layer(dev)
+    steps = min(args.steps, 50)
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        ms = statistics.mean(time_each_ms(graph.replay, flush, warmup=args.warmup, iters=steps))
+        torch.cuda.synchronize()
+    if not torch.equal(graph_out, out):
+        raise SystemExit(f"{name}: graph replay and eager launch disagree")
+    require_clean_status(device, f"{name}, after the timed steps")
+    row = {"value": cfg.useful_flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+           "config": workload_config(cfg), "clocks": clocks.summary(),
+           "frac_of_bf16_peak": cfg.useful_flops / (ms * 1e-3) / 1e12 / peaks[1]}
+    if with_stages:
+        row["roofline"] = stage_roofline(cfg, layer, dev, flush, max(5, min(args.steps, 20)), peaks)
+    del graph, graph_out, out, dev, layer
+    torch.cuda.empty_cache()
+    return row
+
+
+def reference_gpu_row(workload: str) -> dict:
+    """The reference's own CUDA kernels (compiled for sm_100 by oracle/build_ref_ext.py) on this GPU, as a
+    comparison row measured in a child process, so that this process never loads them."""
+    import subprocess
+
+    try:
+        proc = subprocess.run([sys.executable, str(ROOT / "bench_baselines.py"), "--reference-gpu", workload],
+                              capture_output=True, text=True, timeout=300, cwd=ROOT)
+        for text in reversed(proc.stdout.splitlines()):
+            if text.startswith("{"):
+                return json.loads(text)
+        return {"unavailable": f"no result (exit code {proc.returncode}): {proc.stderr[-200:]}"}
+    except Exception as exc:  # noqa: BLE001 - a comparison row, never fatal
+        return {"unavailable": repr(exc)[:200]}
 
 
 def run_single_gpu(args: argparse.Namespace) -> None:
-    from sparsebench_b200 import _C, moe_forward, route_device
-    from sparsebench_b200.spmm import combine, dsd, sdd
-    from sparsebench_b200.timing import l2_flush_buffer, marginal_stage_times_ms, time_each_ms
+    from sparsebench_b200 import moe_forward
+    from sparsebench_b200.timing import l2_flush_buffer, time_each_ms
 
     cfg = CONFIGS[args.workload or "fine_grained"]
     torch.cuda.set_device(0)
@@ -278,25 +480,19 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     layer = make_layer(cfg, seed=0)
     dev = layer.to(device)
     flush = l2_flush_buffer(device)
-    hbm_gbs, bf16_tflops, peak_kind = measured_peaks()
+    peaks = measured_peaks()
+    hbm_gbs, bf16_tflops, peak_kind = peaks
 
-    # ---- correctness gate on a subset of rows before timing anything -------------------------------
-    out = moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
-    torch.cuda.synchronize()
-    if int(_C.device_status(device).item()) != 0:
-        raise RuntimeError("device status is non-zero: a bounded device-side wait expired")
+    # ---- correctness gate before timing anything: every output row against the reference's CPU layer ------
+    graph, graph_out, out = capture_layer(dev)
+    require_clean_status(device, "first layer call")
+    baseline, parity = (None, {"ok": None, "reason": "--no-cpu-baseline"})
+    if not args.no_cpu_baseline:
+        baseline, parity = cpu_baseline(cfg, layer, out)
+        if not parity["ok"]:
+            raise SystemExit(f"the layer's output differs from the reference's CPU layer: {parity}")
 
     # ---- value: graph replay, inputs resident in HBM ------------------------------------------------
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
-    torch.cuda.current_stream().wait_stream(side)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        graph_out = moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
-    torch.cuda.synchronize()
-
     with ClockSampler(0) as clocks:
         torch.cuda.synchronize()
         step_ms = time_each_ms(graph.replay, flush, warmup=args.warmup, iters=args.steps)
@@ -308,7 +504,8 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     dirty_ms = time_each_ms(graph.replay, flush, warmup=3, iters=min(args.steps, 50), leave_l2_dirty=True)
     ms_per_step_dirty_l2 = sum(dirty_ms) / len(dirty_ms)
     if not torch.equal(graph_out, out):
-        raise RuntimeError("graph replay and eager launch disagree")
+        raise SystemExit("graph replay and eager launch disagree")
+    require_clean_status(device, "after the timed steps")
 
     # ---- e2e: public API, host buffers, copies inside the timed region -------------------------------
     host_x, host_idx, host_w = (t.pin_memory() for t in (layer.x, layer.expert_idx, layer.expert_weight))
@@ -324,78 +521,25 @@ def run_single_gpu(args: argparse.Namespace) -> None:
     e2e_ms = time_each_ms(e2e_step, flush, warmup=args.warmup, iters=args.steps)
     e2e_latency_ms = sum(e2e_ms) / len(e2e_ms)  # one step alone: copy in, layer, copy out, nothing overlapped
     e2e_ms_per_step = pipelined_e2e_ms(moe_forward, (host_x, host_idx, host_w), (dev.w1, dev.w2), args.warmup, args.steps)
+    require_clean_status(device, "after the end-to-end steps")
     h2d = host_x.numel() * host_x.element_size() + host_idx.numel() * host_idx.element_size() + \
         host_w.numel() * host_w.element_size()
     d2h = host_out.numel() * host_out.element_size()
 
-    # ---- per-kernel durations, each launch timed alone with events on the launching stream -----------
-    topo = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
-    # As the layer runs them: padding-only groups of 32 rows neither stored nor loaded.
-    h = sdd(dev.x, dev.w1, topo, skip_padding_rows=True)
-    w2_cat = dev.w2.view(cfg.num_experts * cfg.ffn_dim, cfg.d_model)
-    y = dsd(h, w2_cat, topo, version=5, skip_padding_rows=True)
-    iters = max(5, min(args.steps, 50))
-    # Each kernel's time in its place in the layer: differences between the graphs of the first j stages
-    # (see marginal_stage_times_ms).
-    def stage_route(state: dict) -> None:
-        state["topo"] = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
-
-    def stage_sdd(state: dict) -> None:
-        state["h"] = sdd(dev.x, dev.w1, state["topo"], skip_padding_rows=True)
-
-    def stage_dsd(state: dict) -> None:
-        state["y"] = dsd(state["h"], w2_cat, state["topo"], version=5, skip_padding_rows=True)
-
-    def stage_combine(state: dict) -> None:
-        state["out"] = combine(state["y"], dev.expert_weight, state["topo"])
-
-    stage_ms = marginal_stage_times_ms([("routing", stage_route), ("sdd", stage_sdd), ("dsd", stage_dsd),
-                                        ("combine", stage_combine)], flush, 3, iters)
-    stage_timing = ("each kernel in its place in the layer: CUDA-graph replays of the first j stages (each closed by the "
-                    "same one-element kernel), CUDA events around every replay, L2 flushed before it, stage j = "
-                    "prefix j - prefix j-1")
-    rows = live_rows(layer.expert_idx, cfg.num_experts)            # executed by the tensor cores
-    rows_moved = live_rows(layer.expert_idx, cfg.num_experts, 32)  # stored / loaded
-    n_copies = cfg.num_tokens * cfg.k
-    weight_bytes = cfg.num_experts * cfg.d_model * cfg.ffn_dim * 2
-    stage_bytes = {
-        "sdd": cfg.num_tokens * cfg.d_model * 2 + weight_bytes + rows_moved * cfg.ffn_dim * 2,
-        "dsd": rows_moved * cfg.ffn_dim * 2 + weight_bytes + rows_moved * cfg.d_model * 2,
-        "combine": n_copies * cfg.d_model * 2 + n_copies * 6 + cfg.num_tokens * cfg.d_model * 2,
-    }
-    stage_flops = {"sdd": 2 * n_copies * cfg.d_model * cfg.ffn_dim, "dsd": 2 * n_copies * cfg.d_model * cfg.ffn_dim}
-    dominant = max(("sdd", "dsd"), key=lambda s: stage_ms[s])
-    t_dom = stage_ms[dominant] * 1e-3
-    hbm_time = stage_bytes[dominant] / (hbm_gbs * 1e9)
-    tensor_time = 4 * rows * cfg.d_model * cfg.ffn_dim / 2 / (bf16_tflops * 1e12)  # executed flops, padding included
-    if hbm_time >= tensor_time:
-        achieved = stage_bytes[dominant] / t_dom / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs}
-    else:
-        achieved = 2 * rows * cfg.d_model * cfg.ffn_dim / t_dom / 1e12
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_tflops, "unit": "TFLOP/s",
-                    "frac": achieved / bf16_tflops}
-    roofline.update({
-        "kernel": f"bsr_gemm_kernel<{dominant}>", "peak_source": f"{peak_kind} (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback",
-        "launch_ms": stage_ms[dominant], "algorithmic_bytes": stage_bytes[dominant], "live_rows": rows,
-        "rows_moved": rows_moved, "traffic": NCU_TRAFFIC_BYTES.get((cfg.name, dominant)),
-        "stages_ms": stage_ms, "stages_timing": stage_timing,
-        "stages_frac_of_hbm_peak": {s: stage_bytes[s] / (stage_ms[s] * 1e-3) / 1e9 / hbm_gbs for s in stage_bytes},
-        "stages_useful_tflops": {s: stage_flops[s] / (stage_ms[s] * 1e-3) / 1e12 for s in stage_flops},
-    })
+    roofline = stage_roofline(cfg, layer, dev, flush, max(5, min(args.steps, 50)), peaks)
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens": cfg.num_tokens, "d_model": cfg.d_model, "ffn_dim": cfg.ffn_dim,
-                   "experts": cfg.num_experts, "top_k": cfg.k, "routing": cfg.routing, "block_size": 128,
-                   "launch": "one CUDA-graph replay per step (4 kernels)",
+        "config": workload_config(cfg),
+        "method": {"launch": "one CUDA-graph replay per step (4 kernels)",
                    "l2": "before every step 256 MiB are written and then read back, so L2 starts cold and clean (a "
                          "write alone leaves 126 MB of dirty lines that the step would have to write back: "
-                         "ms_per_step_dirty_l2); the 1.07 GB of expert weights also exceed L2",
+                         "ms_per_step_dirty_l2); the expert weights also exceed L2",
                    "ms_per_step_dirty_l2": ms_per_step_dirty_l2,
                    "frac_of_bf16_peak": value / bf16_tflops},
+        "parity": parity,
         "clocks": clocks.summary(),
         "e2e": {"value": cfg.useful_flops / (e2e_ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms_per_step, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -405,31 +549,34 @@ def run_single_gpu(args: argparse.Namespace) -> None:
         "gpu_launches": 4 * args.steps,
         "roofline": roofline,
     }
-    if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(cfg, layer)
+    if baseline is not None:
+        line["cpu_baseline"] = baseline
+    if cfg.name == "fine_grained" and not args.no_library_baselines:
+        import bench_baselines
+
+        line["library_baselines"] = {
+            "what": "the same layer with stock PyTorch kernels on this GPU (eager calls, CUDA events, L2 flushed); "
+                    "context, not the product path",
+            "this_library_eager_ms": statistics.median(time_each_ms(
+                lambda: moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2), flush, 3, 20)),
+            "pipelines": bench_baselines.measure(cfg, dev, flush, out, iters=20),
+        }
+    del graph, graph_out, out, dev
+    torch.cuda.empty_cache()
+    if cfg.name == "fine_grained" and not args.no_library_baselines:
+        line["reference_gpu_kernels"] = reference_gpu_row(cfg.name)
+    if cfg.name == "fine_grained" and not args.no_other_workloads:
+        # The other single-GPU configurations, each with its own clock record (the Mixtral-like one is the
+        # shape that runs into the power cap).
+        line["other_workloads"] = {name: measure_other_workload(name, args, device, flush, peaks)
+                                   for name in ("fine_grained_zipf", "mixtral_like")}
     if cfg.name == "fine_grained" and not args.no_scaling_reference:
         # The multi-GPU runs use the expert-parallel workload (E=128, D=F=2048); its one-GPU value is
         # what their per-GPU throughput should be compared with, so it rides along on this line.
-        del dev, layer, graph, graph_out, out, h, y, topo
-        torch.cuda.empty_cache()
-        ep_cfg = CONFIGS["expert_parallel"]
-        ep_dev = make_layer(ep_cfg, seed=0).to(device)
-        ep_args = (ep_dev.x, ep_dev.expert_idx, ep_dev.expert_weight, ep_dev.w1, ep_dev.w2)
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            moe_forward(*ep_args)
-        torch.cuda.current_stream().wait_stream(side)
-        ep_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(ep_graph):
-            ep_out = moe_forward(*ep_args)
-        ep_steps = min(args.steps, 50)
-        ep_ms = statistics.mean(time_each_ms(ep_graph.replay, flush, warmup=args.warmup, iters=ep_steps))
-        line["expert_parallel_1gpu"] = {
-            "value": ep_cfg.useful_flops / (ep_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ep_ms, "steps": ep_steps,
-            "workload": ep_cfg.name, "how": "the plain layer (all 128 experts on this GPU, no exchange), one graph replay per step",
-        }
-        del ep_graph, ep_out, ep_dev, ep_args
+        row = measure_other_workload("expert_parallel", args, device, flush, peaks, with_stages=False)
+        row["how"] = "the plain layer (all 128 experts on this GPU, no exchange), one graph replay per step"
+        row["workload"] = "expert_parallel"
+        line["expert_parallel_1gpu"] = row
     print(json.dumps(line))
 
 
@@ -447,9 +594,9 @@ def run_profile(args: argparse.Namespace) -> None:
 
 
 def run_expert_parallel(args: argparse.Namespace) -> None:
-    from sparsebench_b200 import ep_bench
+    import bench_ep
 
-    ep_bench.run(args, METRIC, measured_peaks(), ClockSampler)
+    bench_ep.run(args, METRIC, measured_peaks(), ClockSampler)
 
 
 def main() -> None:
@@ -460,6 +607,10 @@ def main() -> None:
     parser.add_argument("--workload", default=None, choices=sorted(CONFIGS))
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-other-workloads", action="store_true",
+                        help="skip the fine_grained_zipf and mixtral_like runs that ride along at N=1")
+    parser.add_argument("--no-library-baselines", action="store_true",
+                        help="skip the stock-PyTorch pipelines (torch._grouped_mm, per-expert loop, padded bmm) at N=1")
     parser.add_argument("--no-scaling-reference", action="store_true",
                         help="skip the one-GPU run of the expert-parallel workload that rides along at N=1")
     parser.add_argument("--ep-capacity-factor", type=float, default=3.0,

@@ -9,19 +9,26 @@ eager launches (config.launch says which).
 
 from __future__ import annotations
 
+import glob
 import json
 import math
 import os
 import sys
+from pathlib import Path
 
 import torch
 import torch.distributed as dist
 
-from sparsebench_b200.ep import ExpertParallelMoE
-from sparsebench_b200.timing import flush_l2, l2_flush_buffer
-from sparsebench_b200.workloads import CONFIGS, make_layer
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
 
-NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer copy on this pool; 900 nominal
+from sparsebench_b200.ep import ExpertParallelMoE  # noqa: E402
+from sparsebench_b200.timing import flush_l2, l2_flush_buffer  # noqa: E402
+from sparsebench_b200.workloads import CONFIGS, _weights, make_layer  # noqa: E402
+
+NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer-to-peer copy bandwidth of one B200 over NVLink 5; 900 nominal
+PARITY_ROWS_PER_RANK = 32
 
 # Micro-batches per step by rank count, where measured to pay (the owner's matmuls tensor-bound and the
 # exchange a large share of the step); elsewhere the step runs whole.
@@ -62,18 +69,48 @@ def _timed_steps(step, flush: torch.Tensor, warmup: int, steps: int, world: int)
     return float(total.item()) / steps
 
 
-def _pipelined_e2e_ms(step, result_of, dev_inputs, host_inputs, warmup: int, steps: int, world: int) -> float:
+class PackedStaging:
+    """One pinned host buffer per direction and one device staging buffer per buffer set, holding the
+    step's inputs back to back (each part 256-byte aligned), so that a step is ONE host->device copy and
+    ONE device->host copy instead of one per tensor. Device-side views give the parts their shapes."""
+
+    def __init__(self, tensors: list[torch.Tensor], device: torch.device) -> None:
+        self.offsets, total = [], 0
+        for t in tensors:
+            self.offsets.append(total)
+            total += (t.numel() * t.element_size() + 255) // 256 * 256
+        self.host = torch.empty(total, dtype=torch.uint8).pin_memory()
+        for t, off in zip(tensors, self.offsets):
+            nbytes = t.numel() * t.element_size()
+            self.host[off:off + nbytes].copy_(t.contiguous().view(-1).view(torch.uint8))
+        self.shapes = [(t.shape, t.dtype) for t in tensors]
+        self.device, self.total = device, total
+
+    def device_buffer(self) -> torch.Tensor:
+        return torch.empty(self.total, dtype=torch.uint8, device=self.device)
+
+    def views(self, buffer: torch.Tensor) -> list[torch.Tensor]:
+        out = []
+        for off, (shape, dtype) in zip(self.offsets, self.shapes):
+            nbytes = int(torch.tensor(shape).prod().item()) * torch.empty(0, dtype=dtype).element_size()
+            out.append(buffer[off:off + nbytes].view(dtype).view(shape))
+        return out
+
+
+def _pipelined_e2e_ms(step, result_of, dev_inputs, staging: PackedStaging, warmup: int, steps: int, world: int) -> float:
     """Mean ms per step, max over ranks, of the step fed from pinned HOST buffers when consecutive steps
     overlap the way a serving loop runs them: three streams (copy in, step, copy out) and two sets of
     staging buffers. `step` reads fixed device tensors (a captured graph does), so the compute stream
     first copies the staged inputs into them (device to device, a few us) and the result out into the
-    set's staging tensor. Every step's host->device and device->host copies are inside the timed region."""
+    set's staging tensor. Every step's host->device copy (one packed buffer) and device->host copy are
+    inside the timed region."""
     device = dev_inputs[0].device
     copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
     sets = []
     for _ in range(2):
+        staged = staging.device_buffer()
         sets.append({
-            "in": [torch.empty_like(t) for t in dev_inputs],
+            "staged": staged, "in": staging.views(staged),
             "out": torch.empty_like(dev_inputs[0]),
             "host_out": torch.empty(dev_inputs[0].shape, dtype=dev_inputs[0].dtype).pin_memory(),
             "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "copied": torch.cuda.Event(),
@@ -84,14 +121,13 @@ def _pipelined_e2e_ms(step, result_of, dev_inputs, host_inputs, warmup: int, ste
             b = sets[i % 2]
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(b["computed"])  # the step that last read this set's inputs is done
-                for staged, host in zip(b["in"], host_inputs):
-                    staged.copy_(host, non_blocking=True)
+                b["staged"].copy_(staging.host, non_blocking=True)
                 b["loaded"].record(copy_in)
             with torch.cuda.stream(compute):
                 compute.wait_event(b["loaded"])
                 compute.wait_event(b["copied"])  # this set's result tensor has been read out
-                for fixed, staged in zip(dev_inputs, b["in"]):
-                    fixed.copy_(staged, non_blocking=True)
+                for fixed, part in zip(dev_inputs, b["in"]):
+                    fixed.copy_(part, non_blocking=True)
                 b["out"].copy_(result_of(step()), non_blocking=True)
                 b["computed"].record(compute)
             with torch.cuda.stream(copy_out):
@@ -120,15 +156,138 @@ def _pipelined_e2e_ms(step, result_of, dev_inputs, host_inputs, warmup: int, ste
     return float(total.item()) / steps
 
 
+def _cpu_list(text: str) -> set[int]:
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if part:
+            first, _, last = part.partition("-")
+            cpus.update(range(int(first), int(last or first) + 1))
+    return cpus
+
+
+def bind_to_gpu_numa_node(local: int) -> dict:
+    """Restricts THIS process to the CPUs of the NUMA node its GPU hangs off, so that the pinned
+    staging buffers it allocates next are placed in that node's memory (first touch) and the copy
+    engine does not pull every rank's tokens across the socket interconnect. Reads sysfs only; changes
+    nothing outside this process. Returns what it found for the JSON line."""
+    info: dict = {"numa_node": None, "bound": False}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        physical = int(visible.split(",")[local]) if visible and visible.replace(",", "").isdigit() else local
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(physical)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
+        info["numa_node"] = node
+        nodes = sorted(glob.glob("/sys/devices/system/node/node*/cpulist"))
+        info["numa_nodes"] = len(nodes)
+        if node >= 0 and len(nodes) > 1:
+            cpus = _cpu_list(Path(f"/sys/devices/system/node/node{node}/cpulist").read_text()) & os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                info["bound"], info["cpus"] = True, len(cpus)
+    except Exception as exc:  # noqa: BLE001 - placement is an optimisation; say why it was skipped
+        info["skipped"] = repr(exc)[:120]
+    return info
+
+
+def host_link_gbs(device: torch.device, world: int) -> dict:
+    """Host<->device copy bandwidth of pinned memory with ALL ranks copying at the same time (what the
+    end-to-end loop can get at best): per direction, this rank's GB/s reduced to min / sum over ranks."""
+    nbytes = 128 * 1024 * 1024
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    host.fill_(1)
+    dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    out = {}
+    for name, copy in (("h2d", lambda: dev.copy_(host, non_blocking=True)), ("d2h", lambda: host.copy_(dev, non_blocking=True))):
+        copy()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(4):
+            copy()
+        end.record()
+        end.synchronize()
+        mine = torch.tensor([4 * nbytes / (start.elapsed_time(end) * 1e-3) / 1e9], dtype=torch.float64, device=device)
+        total, least = mine.clone(), mine.clone()
+        if world > 1:
+            dist.all_reduce(total, op=dist.ReduceOp.SUM)
+            dist.all_reduce(least, op=dist.ReduceOp.MIN)
+        out[name] = {"all_ranks_gbs": float(total.item()), "slowest_rank_gbs": float(least.item())}
+    return out
+
+
+def parity_sample(cfg, layer_in, out: torch.Tensor, world: int, rows: int = PARITY_ROWS_PER_RANK) -> dict:
+    """The first `rows` output rows of THIS rank against the fp32 CPU oracle (rtol = atol = 2e-2), over
+    exactly the experts those tokens use (weights regenerated from their per-expert seeds); the verdicts
+    of all ranks are reduced. The oracle is only the checker here; nothing timed touches it."""
+    from oracle import moe as oracle_moe
+
+    idx = layer_in.expert_idx[:rows]
+    used = sorted(set(idx.reshape(-1).tolist()))
+    position = {e: i for i, e in enumerate(used)}
+    local_idx = torch.tensor([[position[e] for e in row] for row in idx.tolist()])
+    w1 = _weights(0, used, cfg.d_model, cfg.ffn_dim, 0, torch.bfloat16).float()
+    w2 = _weights(1, used, cfg.ffn_dim, cfg.d_model, 0, torch.bfloat16).float()
+    expected = oracle_moe.moe_reference(layer_in.x[:rows].float(), local_idx, layer_in.expert_weight[:rows].float(), w1, w2)
+    got = out[:rows].float().cpu()
+    err = (got - expected).abs()
+    ok = bool((err <= 2e-2 + 2e-2 * expected.abs()).all())
+    verdict = torch.tensor([float(ok), -float(err.max())], dtype=torch.float64, device=out.device)
+    if world > 1:
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    return {"rows_checked": rows * world, "max_abs_err": -float(verdict[1].item()), "ok": bool(verdict[0].item() == 1.0),
+            "against": "fp32 CPU oracle of the layer on each rank's first rows, rtol = atol = 2e-2"}
+
+
+def check_status(moe, device: torch.device, world: int, when: str) -> None:
+    """Raises if any rank's expert-parallel status word or matmul status word is set. Syncs."""
+    from sparsebench_b200 import _C
+
+    words = torch.cat([moe.status.to(torch.int32), _C.device_status(device).to(torch.int32)]).clone()
+    if world > 1:
+        gathered = [torch.empty_like(words) for _ in range(world)]
+        dist.all_gather(gathered, words)
+    else:
+        gathered = [words]
+    problems = []
+    for r, w in enumerate(gathered):
+        ep, gemm = int(w[0].item()), int(w[1].item())
+        if ep & 1:
+            problems.append(f"rank {r}: the exchange overflowed its capacity (rows were dropped)")
+        if ep & 2:
+            problems.append(f"rank {r}: a device-side barrier timed out waiting for a peer rank")
+        if ep & ~3:
+            problems.append(f"rank {r}: expert-parallel status word {ep}")
+        if gemm:
+            problems.append(f"rank {r}: a bounded wait inside a matmul kernel expired (status {gemm})")
+    if problems:
+        raise SystemExit(f"{when}: " + "; ".join(problems))
+
+
+def workload_config(cfg, world: int) -> dict:
+    """The `config` object of the JSON line: the workload only, identical for this arm and the reference arm."""
+    return {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model, "ffn_dim": cfg.ffn_dim,
+            "experts": cfg.num_experts, "top_k": cfg.k, "routing": cfg.routing, "gpus": world}
+
+
 def run(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cls) -> None:
     """Measures the expert-parallel step on every rank; rank 0 prints the JSON line."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    placement = bind_to_gpu_numa_node(local) if world > 1 else {"bound": False}
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     line = measure(args, metric, peaks, clock_sampler_cls, world, rank, local)
+    line.setdefault("e2e", {})["host_placement"] = placement
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -187,11 +346,11 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
 
     out = moe(dev.x, dev.expert_idx, dev.expert_weight)
     torch.cuda.synchronize()
-    overflow = moe.status.clone()
-    if world > 1:
-        dist.all_reduce(overflow, op=dist.ReduceOp.MAX)
-    if int(overflow.item()) != 0:
-        raise SystemExit(f"expert-parallel exchange overflowed {capacity} rows per pair: raise --ep-capacity-factor")
+    check_status(moe, device, world, "first step")
+    # ---- parity gate before anything is timed --------------------------------------------------------
+    parity = parity_sample(cfg, layer_in, out, world)
+    if not parity["ok"]:
+        raise SystemExit(f"expert-parallel output differs from the oracle: {parity}")
 
     # ---- value: graph replay if the collectives capture, else eager --------------------------------
     launch = "eager launches (graph capture of the collectives was refused)"
@@ -226,24 +385,29 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     with clock_sampler_cls(local) as clocks:
         ms_per_step = _timed_steps(step, flush, args.warmup, args.steps, world)
     value = world * cfg.useful_flops / (ms_per_step * 1e-3) / 1e12
+    check_status(moe, device, world, "after the timed steps")
 
     # ---- e2e: public API with host buffers -----------------------------------------------------------
-    host_x, host_idx, host_w = (t.pin_memory() for t in (layer_in.x, layer_in.expert_idx, layer_in.expert_weight))
+    dev_inputs = (dev.x, dev.expert_idx, dev.expert_weight)
+    staging = PackedStaging([layer_in.x, layer_in.expert_idx, layer_in.expert_weight], device)
+    staged_once = staging.device_buffer()
+    staged_views = staging.views(staged_once)
     host_out = torch.empty_like(layer_in.x).pin_memory()
     def e2e_step() -> None:
         # `step` is the captured graph (or the eager call) over dev.x / dev.expert_idx / dev.expert_weight.
-        dev.x.copy_(host_x, non_blocking=True)
-        dev.expert_idx.copy_(host_idx, non_blocking=True)
-        dev.expert_weight.copy_(host_w, non_blocking=True)
+        staged_once.copy_(staging.host, non_blocking=True)
+        for fixed, part in zip(dev_inputs, staged_views):
+            fixed.copy_(part, non_blocking=True)
         result = step()
         host_out.copy_(graph_out if result is None else result, non_blocking=True)
 
     e2e_latency_ms = _timed_steps(e2e_step, flush, args.warmup, args.steps, world)  # one step alone, nothing overlapped
-    e2e_ms = _pipelined_e2e_ms(step, lambda result: graph_out if result is None else result,
-                               (dev.x, dev.expert_idx, dev.expert_weight), (host_x, host_idx, host_w), args.warmup,
-                               args.steps, world)
-    h2d = sum(t.numel() * t.element_size() for t in (host_x, host_idx, host_w))
+    e2e_ms = _pipelined_e2e_ms(step, lambda result: graph_out if result is None else result, dev_inputs, staging,
+                               args.warmup, args.steps, world)
+    check_status(moe, device, world, "after the end-to-end steps")
+    h2d = sum(t.numel() * t.element_size() for t in (layer_in.x, layer_in.expert_idx, layer_in.expert_weight))
     d2h = host_out.numel() * host_out.element_size()
+    host_link = host_link_gbs(device, world)
 
     # ---- per-stage times on this rank (eager, an event at every stage mark) ---------------------------
     # With micro-batches the stages of the parts interleave; the breakdown (and the roofline of the
@@ -296,9 +460,25 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         roofline = {"bound": "tensor", "achieved": achieved, "peak": bf16_tflops, "unit": "TFLOP/s",
                     "frac": achieved / bf16_tflops}
     payload = (world - 1) / world * cfg.num_tokens * cfg.k * cfg.d_model * 2  # useful bytes per direction
+    # Every rank's matmul times and received rows: under skewed routing the step is as slow as its busiest owner.
+    mine = torch.tensor([gemm_ms["sdd"], gemm_ms["dsd"], float(received), float(rows)], dtype=torch.float64, device=device)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(everyone, mine)
+    else:
+        everyone = [mine]
+    table = torch.stack(everyone).cpu()
+    per_rank_stats = {
+        "sdd_ms": [round(v, 4) for v in table[:, 0].tolist()], "dsd_ms": [round(v, 4) for v in table[:, 1].tolist()],
+        "rows_received": [int(v) for v in table[:, 2].tolist()], "rows_padded": [int(v) for v in table[:, 3].tolist()],
+        "matmuls_ms_max_minus_mean": float((table[:, 0] + table[:, 1]).max() - (table[:, 0] + table[:, 1]).mean()),
+    }
+    largest_stage = max(stage_ms, key=stage_ms.get)
     roofline.update({
         "kernel": f"bsr_gemm_kernel<{dominant}> on rank 0", "peak_source": peak_kind, "launch_ms": gemm_ms[dominant],
-        "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "rows_moved": rows_moved, "traffic": None, "stages_ms": stage_ms,
+        "algorithmic_bytes": gemm_bytes[dominant], "live_rows": rows, "rows_moved": rows_moved, "traffic": None,
+        "traffic_note": "no DRAM counter capture of the multi-rank step exists (profilers never wrap a multi-rank command)",
+        "stages_ms": stage_ms, "largest_stage_on_rank0": largest_stage, "per_rank": per_rank_stats,
         "all_to_all": {"useful_bytes_per_direction": payload,
                        "sent_bytes_per_direction": payload if moe.peer is not None else world * moe.capacity * cfg.d_model * 2,
                        "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},
@@ -308,19 +488,19 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model,
-                   "ffn_dim": cfg.ffn_dim, "experts": cfg.num_experts, "experts_per_gpu": per_rank, "top_k": cfg.k,
-                   "routing": cfg.routing, "parallelism": f"ep{world}", "capacity_rows_per_pair": moe.capacity,
+        "config": workload_config(cfg, world),
+        "method": {"parallelism": f"ep{world}", "experts_per_gpu": per_rank, "capacity_rows_per_pair": moe.capacity,
                    "exchange": exchange, "return_leg": "stored by the DSD epilogue" if fused_return else "separate kernel",
-                   "micro_batches": timed_moe.micro_batches,
+                   "dispatch_leg": dispatch_leg, "micro_batches": timed_moe.micro_batches,
                    "launch": launch, "l2": "256 MiB written and read back before every step (L2 cold and clean)",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
+        "parity": parity,
         "clocks": clocks.summary(),
         "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "how": "steps pipelined over three streams (copy in, step, copy out), two sets of staging buffers; "
                        "every step's H2D and D2H copies are inside the timed region",
-                "single_step_latency_ms": e2e_latency_ms},
+                "single_step_latency_ms": e2e_latency_ms, "host_link_all_ranks_copying": host_link},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": roofline,
     }

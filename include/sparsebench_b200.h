@@ -187,7 +187,9 @@ int sb_router_topk(const void* logits, int logits_dtype, int64_t num_tokens, int
  *
  * sb_remap_rows: row_token[r] = row_copy[r] >= 0 ? token_of_copy[row_copy[r]] : -1, turning the
  * copy indices k = 1 routing leaves in row_token into token indices (moe.py:78-81). May run in
- * place (row_token == row_copy). token_of_copy is int32 or int64.
+ * place (row_token == row_copy). token_of_copy is int32 or int64. A token id outside
+ * [0, num_tokens) becomes -1: its row is treated as padding and SDD never reads past x (the
+ * reference's PyTorch indexing raises a device-side assert for such an id).
  *
  * sb_combine_assigned: out[t][:] = bf16( sum over copies c of token t of
  * float(y[copy_row[c]][:]) * float(weight[c]) ), zero for a token without copies (moe.py:87-91).
@@ -196,7 +198,7 @@ int sb_router_topk(const void* logits, int logits_dtype, int64_t num_tokens, int
  * weight_dtype: 0 = bf16, 1 = fp32. d_model % 4 == 0.
  */
 int sb_remap_rows(const int32_t* row_copy, const void* token_of_copy, int token_is_i64, int32_t* row_token,
-                  int64_t num_rows, int64_t num_copies, sb_stream_t stream);
+                  int64_t num_rows, int64_t num_copies, int64_t num_tokens, sb_stream_t stream);
 int sb_combine_assigned(const void* y, const int32_t* copy_row, const void* token_of_copy, int token_is_i64,
                         const void* weight, int weight_dtype, float* accumulator, void* out, int64_t num_copies,
                         int64_t num_tokens, int32_t d_model, sb_stream_t stream);

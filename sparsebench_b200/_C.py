@@ -220,8 +220,9 @@ def router_topk_cuda(logits: torch.Tensor, k: int, index_dtype: torch.dtype = to
 
 # ---- the layer on a flat assignment list (PyTorch ops in the reference, sparsebench/moe.py:59-91) ---
 
-def remap_rows_cuda(row_copy: torch.Tensor, token_of_copy: torch.Tensor) -> torch.Tensor:
-    """row_token[r] = token_of_copy[row_copy[r]] where row_copy[r] >= 0, else -1."""
+def remap_rows_cuda(row_copy: torch.Tensor, token_of_copy: torch.Tensor, num_tokens: int) -> torch.Tensor:
+    """row_token[r] = token_of_copy[row_copy[r]] where row_copy[r] >= 0 and the token lies in
+    [0, num_tokens), else -1."""
     lib = _lib.load()
     _check_index(row_copy, "row_copy")
     _check(token_of_copy.is_cuda and token_of_copy.dim() == 1 and token_of_copy.is_contiguous() and
@@ -230,7 +231,7 @@ def remap_rows_cuda(row_copy: torch.Tensor, token_of_copy: torch.Tensor) -> torc
         out = torch.empty_like(row_copy)
         if row_copy.numel() > 0:
             _lib.check(lib.sb_remap_rows(_ptr(row_copy), _ptr(token_of_copy), int(token_of_copy.dtype == torch.int64),
-                                         _ptr(out), row_copy.numel(), token_of_copy.numel(), _stream()))
+                                         _ptr(out), row_copy.numel(), token_of_copy.numel(), num_tokens, _stream()))
     return out
 
 

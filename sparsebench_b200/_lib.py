@@ -32,7 +32,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P, _P]),
     "sb_combine": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int32, c_int32, _P]),
     "sb_router_topk": (c_int, [_P, c_int, c_int64, c_int32, c_int32, _P, c_int, _P, _P]),
-    "sb_remap_rows": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, _P]),
+    "sb_remap_rows": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, c_int64, _P]),
     "sb_combine_assigned": (c_int, [_P, _P, _P, c_int, _P, c_int, _P, _P, c_int64, c_int64, c_int32, _P]),
     "sb_ep_plan": (c_int, [_P, _P, _P, c_int64, c_int32, c_int32, c_int32, _P, _P, _P, _P]),
     "sb_ep_slot_experts": (c_int, [_P, c_int32, c_int32, c_int32, _P, _P]),

@@ -3,7 +3,10 @@
 // reference does these two steps with PyTorch ops (sparsebench/moe.py:78-81 and :87-91):
 //
 //   sb_remap_rows        routing ran with k = 1, so its row_token holds COPY indices; turn them
-//                        into token indices: out[r] = row_copy[r] >= 0 ? token_of_copy[row_copy[r]] : -1
+//                        into token indices: out[r] = row_copy[r] >= 0 ? token_of_copy[row_copy[r]] : -1.
+//                        A token id outside [0, num_tokens) also becomes -1 (the row is computed as
+//                        padding and the copy contributes nothing), so that SDD never gathers past x;
+//                        the reference's PyTorch indexing raises a device-side assert there instead.
 //   sb_combine_assigned  out[token_of_copy[c]] += float(y[copy_row[c]]) * weight[c] in an fp32
 //                        accumulator (atomic adds, like index_add_), then one rounding to bf16.
 
@@ -19,11 +22,13 @@ constexpr int kThreads = 256;
 template <typename index_t>
 __global__ void __launch_bounds__(kThreads)
 remap_rows_kernel(const int32_t* __restrict__ row_copy, const index_t* __restrict__ token_of_copy,
-                  int32_t* __restrict__ row_token, int64_t num_rows, int64_t num_copies) {
+                  int32_t* __restrict__ row_token, int64_t num_rows, int64_t num_copies, int64_t num_tokens) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < num_rows; r += stride) {
     const int32_t c = row_copy[r];
-    row_token[r] = (c >= 0 && c < num_copies) ? static_cast<int32_t>(token_of_copy[c]) : -1;
+    int64_t token = -1;
+    if (c >= 0 && c < num_copies) token = static_cast<int64_t>(token_of_copy[c]);
+    row_token[r] = (token >= 0 && token < num_tokens) ? static_cast<int32_t>(token) : -1;
   }
 }
 
@@ -80,20 +85,21 @@ unsigned blocks_for(int64_t items, const DeviceInfo* info) {
 extern "C" {
 
 int sb_remap_rows(const int32_t* row_copy, const void* token_of_copy, int token_is_i64, int32_t* row_token,
-                  int64_t num_rows, int64_t num_copies, sb_stream_t stream) {
+                  int64_t num_rows, int64_t num_copies, int64_t num_tokens, sb_stream_t stream) {
   using namespace sb;
   clear_error();
   if (!row_copy || !token_of_copy || !row_token) return fail(SB_ERR_INVALID_ARGUMENT, "remap_rows: NULL buffer");
-  if (num_rows <= 0 || num_copies <= 0) return fail(SB_ERR_INVALID_ARGUMENT, "remap_rows: sizes must be positive");
+  if (num_rows <= 0 || num_copies <= 0 || num_tokens <= 0 || num_tokens > INT32_MAX)
+    return fail(SB_ERR_INVALID_ARGUMENT, "remap_rows: sizes must be positive and the token count fit int32");
   const DeviceInfo* info = current_device_info();
   if (info == nullptr) return SB_ERR_CUDA;
   const unsigned blocks = blocks_for(num_rows, info);
   if (token_is_i64)
     remap_rows_kernel<int64_t><<<blocks, kThreads, 0, as_stream(stream)>>>(
-        row_copy, static_cast<const int64_t*>(token_of_copy), row_token, num_rows, num_copies);
+        row_copy, static_cast<const int64_t*>(token_of_copy), row_token, num_rows, num_copies, num_tokens);
   else
     remap_rows_kernel<int32_t><<<blocks, kThreads, 0, as_stream(stream)>>>(
-        row_copy, static_cast<const int32_t*>(token_of_copy), row_token, num_rows, num_copies);
+        row_copy, static_cast<const int32_t*>(token_of_copy), row_token, num_rows, num_copies, num_tokens);
   return check_launch("remap_rows");
 }
 

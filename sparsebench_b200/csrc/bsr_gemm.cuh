@@ -34,6 +34,8 @@
 
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "ptx_sm100.cuh"
 #include "sb_common.cuh"
 
@@ -538,16 +540,17 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 int encode_bf16_2d_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                        const char* what);
 
-// Opt-in to the large dynamic shared memory of one kernel instance, once per device.
+// Opt-in to the large dynamic shared memory of one kernel instance, once per device. Two host threads
+// may both find the flag clear and both set the attribute (harmless: same value); the flag itself is atomic.
 template <GemmOp kOp, int kTileN>
 int prepare_gemm_kernel(int device) {
-  static bool done[kMaxDevices] = {};
-  if (done[device]) return SB_OK;
+  static std::atomic<bool> done[kMaxDevices] = {};
+  if (done[device].load(std::memory_order_acquire)) return SB_OK;
   const cudaError_t err =
       cudaFuncSetAttribute(bsr_gemm_kernel<kOp, kTileN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            GemmConfig<kOp, kTileN>::kSmemBytes);
   if (err != cudaSuccess) return fail(SB_ERR_CUDA, "shared memory opt-in: %s", cudaGetErrorString(err));
-  done[device] = true;
+  done[device].store(true, std::memory_order_release);
   return SB_OK;
 }
 

@@ -6,6 +6,11 @@
 // One warp per token. Lane l keeps logits l, l+32, ... (up to 32 of them, E <= 1024) in registers;
 // each of the k rounds takes the warp-wide maximum (lowest expert id on equal values) by shuffles and
 // retires it. The softmax runs in fp32 on the k winners and is rounded to the logits' type.
+//
+// Order of the values is torch.topk's: NaN ranks above everything (a NaN logit is picked first and
+// makes the token's weights NaN, as torch.softmax does), -inf is an ordinary smallest value. The k
+// picks are always k DIFFERENT valid expert ids, also for a row of all -inf or all NaN (lowest ids
+// first there; torch leaves that order unspecified).
 
 #include <cuda_bf16.h>
 
@@ -32,6 +37,14 @@ __device__ __forceinline__ void store_weight<float>(float* p, float w) { *p = w;
 template <>
 __device__ __forceinline__ void store_weight<__nv_bfloat16>(__nv_bfloat16* p, float w) { *p = __float2bfloat16_rn(w); }
 
+// Does candidate (a, ia) rank before (b, ib)? NaN first, then larger value, then lower id.
+__device__ __forceinline__ bool ranks_before(float a, int32_t ia, float b, int32_t ib) {
+  const bool an = a != a, bn = b != b;
+  if (an != bn) return an;
+  if (!an && a != b) return a > b;
+  return ia < ib;
+}
+
 template <typename logit_t, typename index_t, int kPerLane>
 __global__ void __launch_bounds__(kThreads)
 router_topk_kernel(const logit_t* __restrict__ logits, int64_t num_tokens, int32_t num_experts, int32_t k,
@@ -49,6 +62,7 @@ router_topk_kernel(const logit_t* __restrict__ logits, int64_t num_tokens, int32
     }
     float picked[kMaxK];
     int32_t picked_id[kMaxK];
+    uint32_t retired = 0;  // bit j: this lane's j-th logit has been picked
     for (int r = 0; r < k; ++r) {
       // Best of this lane (lowest id among equals: ids grow with j), then of the warp.
       float best = -INFINITY;
@@ -56,7 +70,7 @@ router_topk_kernel(const logit_t* __restrict__ logits, int64_t num_tokens, int32
 #pragma unroll
       for (int j = 0; j < kPerLane; ++j) {
         const int32_t e = lane + 32 * j;
-        if (e < num_experts && (v[j] > best || (v[j] == best && e < best_id))) {
+        if (e < num_experts && !((retired >> j) & 1u) && ranks_before(v[j], e, best, best_id)) {
           best = v[j];
           best_id = e;
         }
@@ -65,18 +79,14 @@ router_topk_kernel(const logit_t* __restrict__ logits, int64_t num_tokens, int32
       for (int d = 16; d > 0; d >>= 1) {
         const float other = __shfl_xor_sync(0xffffffffu, best, d);
         const int32_t other_id = __shfl_xor_sync(0xffffffffu, best_id, d);
-        if (other > best || (other == best && other_id < best_id)) {
+        if (ranks_before(other, other_id, best, best_id)) {
           best = other;
           best_id = other_id;
         }
       }
       picked[r] = best;
       picked_id[r] = best_id;
-      if ((best_id & 31) == lane) {
-#pragma unroll
-        for (int j = 0; j < kPerLane; ++j)
-          if (j == (best_id >> 5)) v[j] = -INFINITY;  // retired
-      }
+      if ((best_id & 31) == lane) retired |= 1u << (best_id >> 5);
     }
     // Softmax over the k winners, fp32; picked[0] is the maximum.
     float denom = 0.0f;

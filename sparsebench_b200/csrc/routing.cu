@@ -25,6 +25,8 @@
 
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "sb_common.cuh"
 
 namespace sb {
@@ -432,13 +434,13 @@ int launch_cluster(int device, int blocks, size_t smem, cudaStream_t stream, con
                    int32_t k, int32_t num_experts, int32_t id_bits, int32_t ffn_blocks, int32_t block_size,
                    int32_t max_row_blocks, int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* copy_row,
                    LayoutOut layout, int32_t* error) {
-  static bool attr_done[kMaxDevices] = {};
+  static std::atomic<bool> attr_done[kMaxDevices] = {};  // a lost race only repeats the same attribute call
   auto kernel = route_cluster_kernel<index_t, kIters>;
-  if (!attr_done[device]) {
+  if (!attr_done[device].load(std::memory_order_acquire)) {
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(cluster_smem_bytes(kMaxExperts)));
     if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing: shared memory opt-in: %s", cudaGetErrorString(err));
-    attr_done[device] = true;
+    attr_done[device].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(blocks));
@@ -523,17 +525,17 @@ static __device__ __align__(256) int32_t g_route_static_scratch[kStaticScratchBy
 // Device address of the array on the calling thread's current device. The first call on a device
 // asks the runtime for it (cudaGetSymbolAddress, with that device current); later calls read a table.
 int static_scratch_address(void** out) {
-  static void* address[kMaxDevices] = {};
+  static std::atomic<void*> address[kMaxDevices] = {};  // two threads racing here ask twice and store the same value
   int device = 0;
   if (current_device_info(&device) == nullptr) return SB_ERR_CUDA;
-  if (address[device] == nullptr) {
-    void* ptr = nullptr;
+  void* ptr = address[device].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
     const cudaError_t err = cudaGetSymbolAddress(&ptr, g_route_static_scratch);
     if (err != cudaSuccess || ptr == nullptr)
       return fail(SB_ERR_CUDA, "routing (static scratch): cudaGetSymbolAddress: %s", cudaGetErrorString(err));
-    address[device] = ptr;
+    address[device].store(ptr, std::memory_order_release);
   }
-  *out = address[device];
+  *out = ptr;
   return SB_OK;
 }
 

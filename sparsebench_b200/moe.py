@@ -83,7 +83,7 @@ def moe_forward_assigned(
     topo = route_device(expert_of_copy.reshape(-1, 1).contiguous(), num_experts, ffn_dim, BLOCK_SIZE)
     token_of_copy = token_of_copy.contiguous()
     # With k = 1 routing's row_token holds copy indices (-1 for padding): map them to tokens.
-    topo = dataclasses.replace(topo, row_token=_C.remap_rows_cuda(topo.row_token, token_of_copy))
+    topo = dataclasses.replace(topo, row_token=_C.remap_rows_cuda(topo.row_token, token_of_copy, num_tokens))
     h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
     y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True)
     return _C.combine_assigned_cuda(y, topo.copy_row, token_of_copy, weight_of_copy, num_tokens)

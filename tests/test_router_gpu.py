@@ -40,6 +40,34 @@ def test_known_answer() -> None:
     assert torch.all(weight[:, 0] >= weight[:, 1])
 
 
+def test_nan_and_infinite_logits_follow_torch_topk() -> None:
+    # torch.topk ranks NaN above every number; a row short of comparable values still yields k
+    # different, valid expert ids (the routing kernel would otherwise skip the copy and raise its flag).
+    from sparsebench_b200 import route
+
+    inf, nan = float("inf"), float("nan")
+    logits = torch.tensor([
+        [0.5, nan, 2.0, -1.0, 1.0, 0.0, -2.0, 3.0],       # one NaN: picked first, then the maximum
+        [-inf, -inf, 1.0, -inf, -inf, -inf, -inf, -inf],  # one finite value, the rest -inf
+        [-inf] * 8,                                        # nothing comparable
+        [nan] * 8,                                         # all NaN
+        [inf, 1.0, inf, 0.0, 0.0, 0.0, 0.0, 0.0],          # two +inf: lowest id first
+    ])
+    idx, weight = route(logits.cuda(), 2)
+    idx, weight = idx.cpu(), weight.cpu()
+    want_idx, want_weight = M.route(logits, 2)
+    assert idx[0].tolist() == want_idx[0].tolist() == [1, 7]
+    assert idx[1].tolist()[0] == want_idx[1].tolist()[0] == 2
+    assert idx[4].tolist() == [0, 2]
+    for row in range(logits.shape[0]):
+        picks = idx[row].tolist()
+        assert len(set(picks)) == 2 and all(0 <= e < 8 for e in picks), (row, picks)
+        # The picked VALUES are what torch picks (ids may differ only among equal values).
+        assert torch.equal(logits[row][idx[row]].nan_to_num(nan=1e30), logits[row][want_idx[row]].nan_to_num(nan=1e30))
+        assert torch.equal(weight[row].isnan(), want_weight[row].isnan()), (row, weight[row], want_weight[row])
+    torch.testing.assert_close(weight[1], want_weight[1])
+
+
 def test_router_to_layer_without_host_sync() -> None:
     # logits -> picks -> layer, captured in one graph and replayed with new logits.
     from sparsebench_b200 import moe_forward, route

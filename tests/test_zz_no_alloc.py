@@ -5,8 +5,9 @@ part of the library, for callers that have no way to hand over scratch memory: a
 only pass pointers along, or a process that may not call cudaMalloc once it is serving (the call
 synchronises the device, which this path promises never to do). This file checks, through the C ABI,
 that it leaves exactly what sb_route leaves in every output buffer, twice in a row with different
-routing (the shared array still holds the first call's contents when the second one runs), and that
-it refuses sizes the array cannot hold. It is named so that pytest collects it last.
+routing (the shared array still holds the first call's contents when the second one runs), that
+those buffers are also what the CPU oracle of the layout says they must be, and that it refuses
+sizes the array cannot hold. It is named so that pytest collects it last.
 """
 
 import ctypes
@@ -15,6 +16,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import layout as L
 from sparsebench_b200 import _lib
 from tests.cases import routing_case
 
@@ -61,6 +63,11 @@ def test_same_buffers_as_sb_route_two_calls_in_a_row(num_tokens: int, num_expert
         for name, a, b in zip(NAMES, got, expected):
             assert np.array_equal(a, b), f"call {call}: {name} differs from sb_route"
         assert int(got[-1][0]) == call
+        # And against the CPU oracle directly, so that this file stands by itself.
+        want = L.device_layout(idx.cpu(), num_experts, 256, 128)
+        for name, a in zip(NAMES[:-1], got):
+            assert np.array_equal(a, getattr(want, name)), f"call {call}: {name} differs from the oracle"
+        assert int(got[-1][0]) == want.error
 
 
 def test_rejects_what_the_array_cannot_hold() -> None:
