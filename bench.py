@@ -620,6 +620,11 @@ def main() -> None:
     parser.add_argument("--ep-unfused-return", action="store_true",
                         help="N > 1, peer exchange: DSD writes y and a second kernel pushes it (default: the DSD "
                              "epilogue stores the rows into the source ranks' buffers)")
+    parser.add_argument("--ep-unfused-dispatch", action="store_true",
+                        help="N > 1, peer exchange: push all rows and wait for every rank before the owner's routing "
+                             "(default: the owner's SDD kernel pushes the rows and its tiles wait per expert)")
+    parser.add_argument("--no-nccl-context", action="store_true",
+                        help="N > 1: skip the few extra steps with NCCL all-to-all collectives as the exchange")
     parser.add_argument("--ep-micro-batches", type=int, default=0,
                         help="N > 1, peer exchange: cut each step into this many pipelined micro-batches "
                              "(0 = the default for this N)")

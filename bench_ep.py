@@ -30,11 +30,10 @@ from sparsebench_b200.workloads import CONFIGS, _weights, make_layer  # noqa: E4
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer-to-peer copy bandwidth of one B200 over NVLink 5; 900 nominal
 PARITY_ROWS_PER_RANK = 32
 
-# Micro-batches per step by rank count, where measured to pay (the owner's matmuls tensor-bound and the
-# exchange a large share of the step); elsewhere the step runs whole.
-# 8 ranks (16 experts each, the busiest rank tensor-bound): 0.469 ms whole, 0.427 ms in two parts; 2 ranks (64
-# experts each, HBM-bound): 0.335 ms whole, 0.465 ms in two parts.
-DEFAULT_MICRO_BATCHES: dict[int, int] = {8: 2}
+# Micro-batches per step by rank count, where measured to pay; elsewhere the step runs whole. With the dispatch
+# overlapped inside the owner's SDD kernel the exchange already hides behind the matmuls, and every part would
+# stream the owner's expert weights again.
+DEFAULT_MICRO_BATCHES: dict[int, int] = {}
 
 
 
@@ -329,6 +328,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         try:
             moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
                                     fuse_return=not getattr(args, "ep_unfused_return", False),
+                                    fuse_dispatch=not getattr(args, "ep_unfused_dispatch", False),
                                     micro_batches=micro_batches)
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line
@@ -379,7 +379,14 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     # slot experts, routing (1 launch, 3 beyond 262144 slots), SDD, DSD, (pack | [push rows +] barrier), combine.
     route_launches = 1 if world * moe.capacity <= 262144 else 3
     fused_return = moe.peer is not None and moe.fuse_return
-    launches_per_step = (12 if moe.peer is not None else 8) + route_launches - (1 if fused_return else 0)
+    fused_dispatch = moe.peer is not None and moe.fuse_dispatch
+    if fused_dispatch:
+        # sort, plan, dispatch plan (+ counts), barrier, owner layout, SDD with the pushes, DSD (+ return) [, push], barrier, combine
+        launches_per_step = 9 if fused_return else 10
+        dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for their expert's arrival flags"
+    else:
+        launches_per_step = (12 if moe.peer is not None else 8) + route_launches - (1 if fused_return else 0)
+        dispatch_leg = "separate push kernel and a barrier before routing" if moe.peer is not None else "all-to-all collective"
     if moe.micro_batches > 1:
         launches_per_step = launches_per_step * moe.micro_batches + 1  # every part is a whole step, plus the concatenation
     with clock_sampler_cls(local) as clocks:
@@ -415,7 +422,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     timed_moe = moe
     if moe.micro_batches > 1:
         moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
-                                fuse_return=timed_moe.fuse_return)
+                                fuse_return=timed_moe.fuse_return, fuse_dispatch=timed_moe.fuse_dispatch)
     names: list[str] = []
     sums: dict[str, float] = {}
     iters = max(5, min(args.steps, 30))
@@ -484,6 +491,22 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                        "time_at_measured_nvlink_ms": payload / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3},
     })
 
+    # ---- context: the same step with NCCL all-to-all collectives as the exchange (eager, few steps) --------
+    nccl_context = None
+    if world > 1 and timed_moe.peer is not None and not getattr(args, "no_nccl_context", False):
+        try:
+            nccl_capacity = min(n_copies, int(math.ceil(factor * n_copies / world / 128.0)) * 128)
+            nccl_moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=nccl_capacity, exchange="nccl")
+            nccl_steps = min(args.steps, 10)
+            nccl_ms = _timed_steps(lambda: nccl_moe(dev.x, dev.expert_idx, dev.expert_weight), flush, 3, nccl_steps, world)
+            check_status(nccl_moe, device, world, "NCCL-exchange context steps")
+            nccl_context = {"ms_per_step": nccl_ms, "value": world * cfg.useful_flops / (nccl_ms * 1e-3) / 1e12,
+                            "steps": nccl_steps, "capacity_rows_per_pair": nccl_capacity,
+                            "how": "same step, dispatch and return as fixed-capacity NCCL all-to-all collectives, eager launches"}
+            del nccl_moe
+        except SystemExit as exc:
+            nccl_context = {"unavailable": str(exc)[:200]}
+
     line = {
         "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -495,6 +518,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                    "launch": launch, "l2": "256 MiB written and read back before every step (L2 cold and clean)",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
         "parity": parity,
+        "nccl_exchange": nccl_context,
         "clocks": clocks.summary(),
         "e2e": {"value": world * cfg.useful_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -19,6 +19,9 @@
 //               instruction moves four whole 128-byte row segments. Padding rows use the zero-fill
 //               form (no global read). An asynchronous mbarrier arrive reports completion, so the
 //               threads run the full pipeline depth ahead without ever waiting for their data.
+//   warps 14-17 expert-parallel dispatch instance of SDD only (kDispatch): this rank's pushes as a source
+//               of token rows, while the gather warps first wait, per tile, for the tile's expert to
+//               have arrived from every source rank (ep_dispatch.cuh).
 //
 // Shared-memory stage layout (all 1024-byte aligned, as the 128-byte swizzle needs):
 //   A: 128 rows x 128 B; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)      (16 KB)
@@ -36,6 +39,7 @@
 
 #include <atomic>
 
+#include "ep_dispatch.cuh"
 #include "ptx_sm100.cuh"
 #include "sb_common.cuh"
 
@@ -72,9 +76,11 @@ struct GemmParams {
   void* const* peer_out;
   int32_t my_rank;
   int32_t capacity;
+  // SDD as the first step of an expert-parallel owner whose rows are still arriving (kDispatch instance).
+  DispatchParams dispatch;
 };
 
-template <GemmOp kOp, int kTileN>
+template <GemmOp kOp, int kTileN, bool kDispatch = false>
 struct GemmConfig {
   static constexpr int kTileM = 128;
   static constexpr int kTileK = 64;
@@ -89,7 +95,10 @@ struct GemmConfig {
   static constexpr int kGatherWarps = kOp == GemmOp::kSdd ? 4 : 0;
   static constexpr int kFirstEpilogueWarp = 2;
   static constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
-  static constexpr int kThreads = 32 * (kFirstGatherWarp + kGatherWarps);
+  static constexpr int kPushWarps = kDispatch ? 4 : 0;
+  static constexpr int kFirstPushWarp = kFirstGatherWarp + kGatherWarps;
+  static constexpr int kThreads = 32 * (kFirstPushWarp + kPushWarps);
+  static_assert(!kDispatch || kOp == GemmOp::kSdd, "only SDD has a dispatch instance");
   static constexpr int kTmemColumns = 2 * kTileN;              // two accumulators; 256 or 512
   static constexpr int kBarrierBytes = 256;
   static constexpr int kStagingBytes = 32 * 128;               // per epilogue warp: 32 rows x 64 bf16
@@ -119,12 +128,12 @@ __device__ __forceinline__ float gelu_erf(float v) {
   return 0.5f * v * (1.0f + copysignf(erf_abs, x));
 }
 
-template <GemmOp kOp, int kTileN>
-__global__ void __launch_bounds__(GemmConfig<kOp, kTileN>::kThreads, 1)
+template <GemmOp kOp, int kTileN, bool kDispatch = false>
+__global__ void __launch_bounds__(GemmConfig<kOp, kTileN, kDispatch>::kThreads, 1)
 bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_rows32,
                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
-                const GemmParams p) {
-  using Cfg = GemmConfig<kOp, kTileN>;
+                const __grid_constant__ GemmParams p) {
+  using Cfg = GemmConfig<kOp, kTileN, kDispatch>;
   constexpr bool kIsSdd = kOp == GemmOp::kSdd;
 
   extern __shared__ uint8_t smem_raw[];
@@ -455,7 +464,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (acc == 0) acc_phase ^= 1u;
     }
     if (lane == 0) ptx::bulk_wait_all();  // this warp's stores are complete before the CTA retires
-  } else if (kIsSdd) {
+  } else if (kIsSdd && warp < Cfg::kFirstPushWarp) {
     // ---------------------------------------------------------------- A gather (SDD)
     // Lane l = (g, c): g = l >> 3 picks one of four rows, c = l & 7 the 16-byte chunk of the 128-byte
     // K step, so one warp instruction moves four whole 128-byte row segments (coalesced in global
@@ -478,6 +487,10 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       load_tokens(tile, tok);
       cur = load_tile_info(tile);
     }
+    // Dispatch instance: the expert whose rows are known to have arrived from every source, and the
+    // value the arrival flags carry in this step.
+    int32_t arrived_expert = -1;
+    const uint32_t dispatch_epoch = kDispatch ? *p.dispatch.epoch_word : 0u;
     while (ok && tile < total_tiles) {
       // The next tile's record and row -> token table are fetched while this tile is gathered.
       const int32_t next = tile + tile_step;
@@ -488,7 +501,16 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         next_info = load_tile_info(next);
       }
       const bool live = cur.begin != cur.end;
+      const int32_t expert = cur.expert;
       cur = next_info;
+      if (kDispatch && live && expert != arrived_expert) {
+        if (!wait_expert_arrived(p.dispatch, expert, dispatch_epoch, lane, abort_word)) {
+          if (lane == 0) give_up(SB_DEV_TIMEOUT_DISPATCH);
+          break;
+        }
+        __syncwarp();
+        arrived_expert = expert;
+      }
       if (live) {
         const __nv_bfloat16* src[8];
 #pragma unroll
@@ -516,6 +538,14 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tile = next;
     }
     ptx::cp_async_wait_all();
+  } else if (kDispatch) {
+    // ---------------------------------------------------------------- dispatch pushes (this rank as a source)
+    // Chunk c of the push plan goes to worker c mod (4 * grid): consecutive chunks to different thread
+    // blocks, so that the pairs every owner needs first are complete first. These warps wait for
+    // nothing and run to the end of their list even if another role of the block has given up.
+    const int push_warp = warp - Cfg::kFirstPushWarp;
+    push_chunks(p.dispatch, push_warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
+                Cfg::kPushWarps * static_cast<int>(gridDim.x), lane);
   }
 
   // Common exit: every role is done (or has given up); release TMEM.
@@ -542,32 +572,32 @@ int encode_bf16_2d_map(CUtensorMap* map, const void* base, uint64_t rows, uint64
 
 // Opt-in to the large dynamic shared memory of one kernel instance, once per device. Two host threads
 // may both find the flag clear and both set the attribute (harmless: same value); the flag itself is atomic.
-template <GemmOp kOp, int kTileN>
+template <GemmOp kOp, int kTileN, bool kDispatch = false>
 int prepare_gemm_kernel(int device) {
   static std::atomic<bool> done[kMaxDevices] = {};
   if (done[device].load(std::memory_order_acquire)) return SB_OK;
   const cudaError_t err =
-      cudaFuncSetAttribute(bsr_gemm_kernel<kOp, kTileN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           GemmConfig<kOp, kTileN>::kSmemBytes);
+      cudaFuncSetAttribute(bsr_gemm_kernel<kOp, kTileN, kDispatch>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           GemmConfig<kOp, kTileN, kDispatch>::kSmemBytes);
   if (err != cudaSuccess) return fail(SB_ERR_CUDA, "shared memory opt-in: %s", cudaGetErrorString(err));
   done[device].store(true, std::memory_order_release);
   return SB_OK;
 }
 
-template <GemmOp kOp, int kTileN>
+template <GemmOp kOp, int kTileN, bool kDispatch = false>
 int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, const CUtensorMap& map_b,
                 const CUtensorMap& map_out, const GemmParams& params, cudaStream_t stream, const char* what) {
   int device = 0;
   const DeviceInfo* info = current_device_info(&device);
   if (info == nullptr) return SB_ERR_CUDA;
-  if (int rc = prepare_gemm_kernel<kOp, kTileN>(device)) return rc;
-  using Cfg = GemmConfig<kOp, kTileN>;
+  if (int rc = prepare_gemm_kernel<kOp, kTileN, kDispatch>(device)) return rc;
+  using Cfg = GemmConfig<kOp, kTileN, kDispatch>;
   GemmParams launch_params = params;
   if (launch_params.raster_rows < 1) launch_params.raster_rows = 1;
   const int64_t tiles = static_cast<int64_t>(params.num_row_blocks) * params.num_slices;
   const unsigned grid = static_cast<unsigned>(tiles < info->sm_count ? tiles : info->sm_count);
-  bsr_gemm_kernel<kOp, kTileN><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_a_rows32, map_b, map_out,
-                                                                                  launch_params);
+  bsr_gemm_kernel<kOp, kTileN, kDispatch><<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(map_a, map_a_rows32, map_b,
+                                                                                             map_out, launch_params);
   return check_launch(what);
 }
 

@@ -1,0 +1,128 @@
+// Expert-parallel dispatch fused with the owner's first matmul: the device side shared by the SDD
+// kernel's push warps, its gather warps and the stand-alone push kernel.
+//
+// Every rank is a SOURCE of token rows (its T*k copies, sorted by global expert) and an OWNER of
+// E_local experts. Instead of "push all rows, barrier, then compute", rows travel while the owner's
+// tensor cores already work:
+//
+//   source   walks its copies expert-major (local expert 0 of every destination first, then 1, ...),
+//            in chunks of a few rows of one (destination d, local expert e) pair; a warp stores a
+//            chunk's rows straight into d's receive buffer (plain stores through the peer mapping,
+//            i.e. over NVLink), fences, and counts the chunk; whoever completes a pair's last chunk
+//            publishes the step's epoch in d's flag [source][e] with a system-scope release store.
+//   owner    before a gather warp of SDD reads the rows of a tile of local expert e it waits, bounded,
+//            until the flags [s][e] of all sources s carry this step's epoch (acquire loads). Tiles
+//            are walked expert-major too, so the first tiles need what arrives first.
+//
+// Nothing here waits for anything that itself waits: push warps never block, so two ranks' kernels
+// cannot wait for each other in a circle. Flags carry a monotonically growing epoch (the value of the
+// exchange's barrier counter in this step), so they are never reset.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+namespace sb {
+
+constexpr int kPushChunkRows = 4;
+
+struct DispatchParams {
+  // Source side.
+  const uint4* x;                // [T, D] this rank's token rows
+  const int32_t* sorted_token;   // [T*k] token of every sorted position (sort by global expert)
+  // Push plan, four arrays of num_pairs + 1 ints back to back, pair q = e * num_ranks + d:
+  //   chunk_prefix | first_pos (sorted position of the run) | slot_start (first slot i at d) | kept (rows)
+  const int32_t* plan;
+  uint4* const* peer_recv;       // [N] every rank's receive buffer [N * capacity, D]
+  uint32_t* const* peer_flags;   // [N] every rank's arrival flags [N * E_local]
+  uint32_t* done;                // [num_pairs] chunk counters of this rank, zero between kernels
+  // Owner side.
+  const uint32_t* my_flags;      // [N * E_local]
+  // Both: the word whose current value is this step's epoch (the exchange's barrier counter).
+  const uint32_t* epoch_word;
+  int32_t my_rank;
+  int32_t num_ranks;
+  int32_t experts_local;
+  int32_t capacity;
+  int32_t vecs_per_row;          // D * 2 / 16
+  int32_t num_pairs;             // N * E_local
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t dispatch_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// One warp's share of the source side: chunks worker, worker + num_workers, ... of the push plan.
+__device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker, int num_workers, int lane) {
+  const int32_t pairs = dp.num_pairs;
+  const int32_t* chunk_prefix = dp.plan;
+  const int32_t* first_pos = dp.plan + (pairs + 1);
+  const int32_t* slot_start = dp.plan + 2 * (pairs + 1);
+  const int32_t* kept = dp.plan + 3 * (pairs + 1);
+  const int32_t total = __ldg(chunk_prefix + pairs);
+  const uint32_t epoch = *dp.epoch_word;
+  for (int32_t c = worker; c < total; c += num_workers) {
+    int32_t lo = 0, hi = pairs - 1;  // last pair whose first chunk is <= c
+    while (lo < hi) {
+      const int32_t mid = (lo + hi + 1) >> 1;
+      if (__ldg(chunk_prefix + mid) <= c) lo = mid; else hi = mid - 1;
+    }
+    const int32_t q = lo;
+    const int32_t e = q / dp.num_ranks;
+    const int32_t d = q - e * dp.num_ranks;
+    const int32_t first_chunk = __ldg(chunk_prefix + q);
+    const int32_t j0 = (c - first_chunk) * kPushChunkRows;
+    const int32_t rows = min(kPushChunkRows, __ldg(kept + q) - j0);  // <= 0: the one chunk of an empty pair
+    if (rows > 0) {
+      const int32_t pos0 = __ldg(first_pos + q) + j0;
+      uint4* dst = dp.peer_recv[d] +
+                   (static_cast<int64_t>(dp.my_rank) * dp.capacity + __ldg(slot_start + q) + j0) * dp.vecs_per_row;
+      for (int32_t r = 0; r < rows; ++r) {
+        const uint4* src = dp.x + static_cast<int64_t>(__ldg(dp.sorted_token + pos0 + r)) * dp.vecs_per_row;
+        uint4* out = dst + static_cast<int64_t>(r) * dp.vecs_per_row;
+#pragma unroll 8
+        for (int32_t v = lane; v < dp.vecs_per_row; v += 32) out[v] = __ldg(src + v);
+      }
+      __threadfence_system();  // this lane's rows are in the destination's memory before the count below
+    }
+    __syncwarp();
+    if (lane == 0) {
+      const int32_t chunks = __ldg(chunk_prefix + q + 1) - first_chunk;
+      if (atomicAdd(dp.done + q, 1u) + 1u == static_cast<uint32_t>(chunks)) {
+        dp.done[q] = 0u;          // ready for the next step
+        __threadfence_system();   // the other chunks' rows (fenced before their counts) before the flag
+        st_release_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.experts_local + e, epoch);
+      }
+    }
+  }
+}
+
+// Owner side, whole warp: until every source has delivered its rows for local expert e in this step.
+// Lane s watches source s. Returns false when the wait ran out (1 s) or `*abort` was raised.
+__device__ __forceinline__ bool wait_expert_arrived(const DispatchParams& dp, int32_t e, uint32_t epoch, int lane,
+                                                    const volatile uint32_t* abort) {
+  const uint32_t* flag = dp.my_flags + (lane < dp.num_ranks ? lane : 0) * dp.experts_local + e;
+  const uint64_t start = dispatch_timer_ns();
+  for (uint32_t poll = 0;; ++poll) {
+    const bool here = lane >= dp.num_ranks || static_cast<int32_t>(ld_acquire_sys_u32(flag) - epoch) >= 0;
+    if (__all_sync(0xffffffffu, here)) return true;
+    if ((poll & 31u) == 31u) {
+      const bool stop = *abort != 0u || dispatch_timer_ns() - start > 1000ull * 1000ull * 1000ull;
+      if (__any_sync(0xffffffffu, stop)) return false;
+    }
+    __nanosleep(100);
+  }
+}
+
+}  // namespace sb

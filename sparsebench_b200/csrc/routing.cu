@@ -415,6 +415,100 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
                       lane);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel owner: the layout over this rank's receive slots straight from the exchanged
+// counts, without ever looking at the slots. Slot j = s * capacity + i holds the i-th copy that
+// source rank s sent here; a source sends its copies sorted by expert, so the copies of local expert
+// e from source s occupy slots s * capacity + [start_s(e), start_s(e) + counts[s][e]) with start_s the
+// exclusive scan of counts[s][.] (what does not fit in `capacity` is cut off, as the sender cut it).
+// Sorting the slots by expert with a stable sort (what sb_route does when it is handed one expert id
+// per slot, -1 for the empty ones) puts expert e's rows in (source, i) order; this kernel writes
+// exactly those arrays, bit for bit, from N * E_local counts instead of N * capacity ids, in one
+// launch. Every block recomputes the small tables in shared memory and takes a share of the rows.
+// Needs N * E_local <= 1024 (one thread per (source, expert) pair).
+constexpr int kOwnerThreads = 1024;
+
+__global__ void __launch_bounds__(kOwnerThreads, 1)
+ep_owner_layout_kernel(const int32_t* __restrict__ recv_counts, int32_t num_ranks, int32_t experts_local,
+                       int32_t capacity, int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
+                       int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
+                       int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
+  __shared__ int32_t kept[kMaxExperts];        // [s][e] copies of e from s that fit the capacity
+  __shared__ int32_t slot_start[kMaxExperts];  // [s][e] first slot index i of that run
+  __shared__ int32_t row_start[kMaxExperts];   // [s][e] first row of that run in the layout
+  __shared__ int32_t source_total[kMaxExperts];  // [s] slots of source s in use
+  __shared__ int32_t counts[kMaxExperts];      // [e]
+  __shared__ int32_t offsets[kMaxExperts + 1]; // [e] padded start row
+  __shared__ int32_t warp_sums[32];
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int pairs = num_ranks * experts_local;
+  if (tid < num_ranks) {  // one thread per source: scan its counts over the experts, cut at the capacity
+    int32_t running = 0;
+    for (int32_t e = 0; e < experts_local; ++e) {
+      const int32_t c = max(0, recv_counts[tid * experts_local + e]);
+      const int32_t begin = min(capacity, running);
+      const int32_t end = min(capacity, running + c);
+      running = min(capacity, running + c);
+      kept[tid * experts_local + e] = end - begin;
+      slot_start[tid * experts_local + e] = begin;
+    }
+    source_total[tid] = running;
+  }
+  __syncthreads();
+  int32_t total = 0;
+  if (tid < experts_local) {  // one thread per expert: the sources' runs follow one another
+    for (int32_t src = 0; src < num_ranks; ++src) {
+      row_start[src * experts_local + tid] = total;  // relative to the expert's first row for now
+      total += kept[src * experts_local + tid];
+    }
+    counts[tid] = total;
+  }
+  const int32_t padded = tid < experts_local ? (total + block_size - 1) / block_size * block_size : 0;
+  int32_t all_rows = 0;
+  const int32_t start = block_exclusive_scan(padded, warp_sums, &all_rows);
+  if (tid < experts_local) offsets[tid] = start;
+  if (tid == 0) offsets[experts_local] = all_rows;
+  __syncthreads();
+  if (tid < pairs) row_start[tid] += offsets[tid % experts_local];
+  if (blockIdx.x == 0) {
+    if (tid < experts_local) {
+      tokens_per_expert[tid] = counts[tid];
+      padded_offsets[tid] = offsets[tid];
+    }
+    if (tid == 0) {
+      padded_offsets[experts_local] = all_rows;
+      error[0] = 0;
+    }
+  }
+  __syncthreads();
+
+  const int warps_per_block = kOwnerThreads / 32;
+  const int warp_index = static_cast<int>(blockIdx.x) * warps_per_block + (tid >> 5);
+  const int warp_count = static_cast<int>(gridDim.x) * warps_per_block;
+  // Real rows: one warp per (source, expert) run.
+  for (int pair = warp_index; pair < pairs; pair += warp_count) {
+    const int32_t src = pair / experts_local;
+    const int32_t first_slot = src * capacity + slot_start[pair];
+    const int32_t first_row = row_start[pair];
+    for (int32_t j = lane; j < kept[pair]; j += 32) {
+      layout.row_token[first_row + j] = first_slot + j;
+      copy_row[first_slot + j] = first_row + j;
+    }
+  }
+  // Empty slots.
+  const int64_t slots = static_cast<int64_t>(num_ranks) * capacity;
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * kOwnerThreads + tid; j < slots;
+       j += static_cast<int64_t>(gridDim.x) * kOwnerThreads) {
+    const int32_t src = static_cast<int32_t>(j / capacity);
+    if (static_cast<int32_t>(j - static_cast<int64_t>(src) * capacity) >= source_total[src]) copy_row[j] = -1;
+  }
+  // Padding rows, rows past the end and the block-sparse arrays.
+  fill_layout(offsets, counts, experts_local, block_size, ffn_blocks, max_row_blocks, layout, warp_index, warp_count,
+              lane);
+}
+
 size_t cluster_smem_bytes(int32_t num_experts) {
   const size_t e = static_cast<size_t>(num_experts);
   return ((kClusterThreads / 32) * (e + 1) + e + (e + 1) + e + e + 32 + 1) * sizeof(int32_t);
@@ -604,6 +698,37 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
                             max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
   return sb::launch_route(static_cast<const int32_t*>(expert_idx), n_copies, k, num_experts, ffn_blocks, block_size,
                           max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
+}
+
+int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,
+                       int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
+                       int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,
+                       int32_t* row_offsets, int32_t* col_indices, int32_t* error, sb_stream_t stream) {
+  sb::clear_error();
+  if (num_ranks <= 0 || experts_local <= 0 || static_cast<int64_t>(num_ranks) * experts_local > sb::kMaxExperts)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: need 0 < ranks * local experts <= %d", sb::kMaxExperts);
+  if (capacity <= 0 || ffn_blocks <= 0) return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: capacity and ffn_blocks must be positive");
+  int64_t want_rb = 0;
+  if (int rc = sb_route_sizes(static_cast<int64_t>(num_ranks) * capacity, experts_local,
+                              static_cast<int64_t>(ffn_blocks) * block_size, block_size, &want_rb, nullptr, nullptr))
+    return rc;
+  if (want_rb != max_row_blocks)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: max_row_blocks is %d, worst case needs %lld", max_row_blocks,
+                    (long long)want_rb);
+  if (!recv_counts || !tokens_per_expert || !padded_offsets || !row_token || !copy_row || !row_block_expert ||
+      !row_offsets || !col_indices || !error)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: NULL buffer");
+  const sb::DeviceInfo* info = sb::current_device_info();
+  if (info == nullptr) return SB_ERR_CUDA;
+  // Enough blocks that the fills (a few hundred KB) spread over the GPU; every block redoes the small tables.
+  int64_t blocks = (static_cast<int64_t>(num_ranks) * capacity + 8 * sb::kOwnerThreads - 1) / (8 * sb::kOwnerThreads);
+  if (blocks < 1) blocks = 1;
+  if (blocks > info->sm_count) blocks = info->sm_count;
+  const sb::LayoutOut layout{row_token, row_block_expert, row_offsets, col_indices};
+  sb::ep_owner_layout_kernel<<<static_cast<unsigned>(blocks), sb::kOwnerThreads, 0, sb::as_stream(stream)>>>(
+      recv_counts, num_ranks, experts_local, capacity, ffn_blocks, block_size, static_cast<int32_t>(max_row_blocks),
+      tokens_per_expert, padded_offsets, copy_row, layout, error);
+  return sb::check_launch("ep_owner_layout");
 }
 
 int sb_route_static_scratch(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k,

@@ -4,12 +4,15 @@
 
 #include "bsr_gemm.cuh"
 
-extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
-                      const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model,
-                      int32_t ffn_dim, int32_t num_experts, int32_t num_row_blocks, int apply_gelu,
-                      int skip_padding_rows, int32_t* dev_status, sb_stream_t stream) {
-  using namespace sb;
-  clear_error();
+namespace sb {
+namespace {
+
+// dispatch == nullptr: the plain kernel. Otherwise the expert-parallel instance whose extra warps push
+// this rank's rows to their owners and whose gather warps wait for the rows of each tile's expert.
+int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
+               const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
+               int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int skip_padding_rows,
+               const DispatchParams* dispatch, int32_t* dev_status, sb_stream_t stream) {
   if (!x || !w1 || !row_token || !row_block_expert || !row_offsets)
     return fail(SB_ERR_INVALID_ARGUMENT, "sdd: NULL buffer");
   if (num_tokens <= 0 || num_experts <= 0 || num_row_blocks < 0)
@@ -24,7 +27,8 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
   if (w_rows > INT32_MAX || static_cast<int64_t>(ffn_dim) * d_model > INT32_MAX ||
       static_cast<int64_t>(num_row_blocks) * (ffn_dim / 256) > INT32_MAX)
     return fail(SB_ERR_INVALID_ARGUMENT, "sdd: problem too large");
-  if (num_row_blocks == 0) return SB_OK;
+  if (num_row_blocks == 0 && dispatch == nullptr) return SB_OK;
+  if (num_row_blocks == 0) return fail(SB_ERR_INVALID_ARGUMENT, "sdd (dispatch): the owner needs at least one row block");
   if (!h_blocks) return fail(SB_ERR_INVALID_ARGUMENT, "sdd: NULL output");
 
   CUtensorMap map_a{};  // unused by SDD: its A rows are gathered by cp.async
@@ -55,5 +59,56 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
   // so that a W1 tile is read from HBM once per band instead of once per wave (measured on the
   // Mixtral-like shape: 1027 -> 861 us; shapes with ~2 row blocks per expert lose 3-5 % and stay plain).
   params.raster_rows = num_row_blocks >= 4 * num_experts ? 8 : 1;
+  if (dispatch != nullptr) {
+    params.dispatch = *dispatch;
+    return launch_gemm<GemmOp::kSdd, 256, true>(map_a, map_a, map_b, map_out, params, as_stream(stream),
+                                                "sdd (dispatch)");
+  }
   return launch_gemm<GemmOp::kSdd, 256>(map_a, map_a, map_b, map_out, params, as_stream(stream), "sdd");
+}
+
+}  // namespace
+}  // namespace sb
+
+extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
+                      const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model,
+                      int32_t ffn_dim, int32_t num_experts, int32_t num_row_blocks, int apply_gelu,
+                      int skip_padding_rows, int32_t* dev_status, sb_stream_t stream) {
+  sb::clear_error();
+  return sb::sdd_launch(x, w1, row_token, row_block_expert, row_offsets, h_blocks, num_tokens, d_model, ffn_dim,
+                        num_experts, num_row_blocks, apply_gelu, skip_padding_rows, nullptr, dev_status, stream);
+}
+
+extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const int32_t* row_slot,
+                                  const int32_t* row_block_expert, const int32_t* row_offsets, void* h_blocks,
+                                  int32_t d_model, int32_t ffn_dim, int32_t num_row_blocks, const void* x,
+                                  const int32_t* sorted_token, const int32_t* plan, void* const* peer_recv,
+                                  uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
+                                  const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks,
+                                  int32_t experts_local, int32_t capacity, int32_t* dev_status, sb_stream_t stream) {
+  using namespace sb;
+  clear_error();
+  if (!x || !sorted_token || !plan || !peer_recv || !peer_flags || !my_flags || !done || !epoch_word)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: NULL buffer");
+  if (num_ranks <= 0 || num_ranks > 32 || my_rank < 0 || my_rank >= num_ranks || experts_local <= 0 || capacity <= 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: need 0 <= rank < ranks <= 32, local experts > 0, capacity > 0");
+  if (!aligned16(x)) return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: x must be 16-byte aligned");
+  DispatchParams dp{};
+  dp.x = static_cast<const uint4*>(x);
+  dp.sorted_token = sorted_token;
+  dp.plan = plan;
+  dp.peer_recv = reinterpret_cast<uint4* const*>(peer_recv);
+  dp.peer_flags = peer_flags;
+  dp.done = done;
+  dp.my_flags = my_flags;
+  dp.epoch_word = epoch_word;
+  dp.my_rank = my_rank;
+  dp.num_ranks = num_ranks;
+  dp.experts_local = experts_local;
+  dp.capacity = capacity;
+  dp.vecs_per_row = d_model / 8;
+  dp.num_pairs = num_ranks * experts_local;
+  return sdd_launch(recv_rows, w1, row_slot, row_block_expert, row_offsets, h_blocks,
+                    static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, &dp,
+                    dev_status, stream);
 }

@@ -14,10 +14,15 @@ slices of w1/w2 never move) and T local tokens. One step on a rank:
      a smaller C trades traffic for an overflow flag);
   4. the owner derives the local expert of every receive slot from the counts, runs routing
      (k = 1, empty slots skipped), SDD and DSD on the received rows exactly as on one GPU;
-  5. pack each slot's result row, exchange back, and combine with the local gates. With the peer
-     exchange the owner's DSD stores each result row into its source rank's buffer straight from
-     its epilogue (no y, no second kernel), and the step can be cut into micro-batches that overlap
-     one part's exchange with another part's matmuls.
+  5. pack each slot's result row, exchange back, and combine with the local gates.
+
+With the peer exchange both legs ride inside the owner's matmul kernels. Dispatch: only the
+per-expert COUNTS are exchanged up front (they are all the owner's layout needs); the rows are
+pushed by extra warps of the SDD kernel itself, expert by expert, and every SDD tile waits, bounded,
+for the arrival flags of its expert, so the rows travel while the tensor cores already work on what
+has arrived. Return: the DSD epilogue stores each result row into its source rank's buffer (no y, no
+second kernel). Two device-side barriers remain per step: a light one after the counts, and the
+one before the combine.
 
 Slots arrive ordered by (source rank, expert, copy index), and the owner's sort is stable, so
 within an expert rows follow (source rank, copy index): the global copy order with global token
@@ -109,13 +114,35 @@ class CudaOps:
 
         _C.ep_barrier(peer_pads, my_pad, epoch, my_rank, status)
 
+    def dispatch_plan(self, expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts):
+        """The source's push plan; also stores this rank's counts into every owner's table."""
+        from sparsebench_b200 import _C
+
+        return _C.ep_dispatch_plan(expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts)
+
+    def owner_layout(self, recv_counts: torch.Tensor, capacity: int, ffn_dim: int):
+        """The owner's layout over its receive slots from the exchanged counts alone."""
+        from sparsebench_b200 import _C
+        from sparsebench_b200.routing import DeviceTopology
+
+        out = _C.ep_owner_layout(recv_counts, capacity, ffn_dim, BLOCK_SIZE)
+        return DeviceTopology(BLOCK_SIZE, recv_counts.shape[1], ffn_dim // BLOCK_SIZE, *out)
+
+    def sdd_dispatch(self, peer, w1, topo, x, sorted_token, plan, my_rank, capacity):
+        """SDD over rows that are still arriving, with this rank's own pushes in the same kernel."""
+        from sparsebench_b200 import _C
+
+        return _C.ep_sdd_dispatch(peer.recv, w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
+                                  topo.col_indices.numel(), x, sorted_token, plan, peer.peer_recv, peer.peer_flags,
+                                  peer.flags, peer.done, peer.epoch, my_rank, capacity)
+
 
 class PeerExchange:
     """Exchange buffers of one rank mapped into every other rank (torch symmetric memory: CUDA VMM
     handles exchanged once at set-up), so that rows are stored straight into their owner's memory
     over NVLink and only real rows travel. Holds, per rank: recv [N*C, D] (dispatched rows, block s
-    from rank s), ret [N*C, D] (results coming back, block d from rank d), counts [N, E/N] and a pad
-    of N words for the device-side barrier."""
+    from rank s), ret [N*C, D] (results coming back, block d from rank d), counts [N, E/N], a pad
+    of N words for the device-side barrier and N * E/N arrival flags (one per source and local expert)."""
 
     def __init__(self, group: dist.ProcessGroup, device: torch.device, capacity: int, d_model: int,
                  experts_local: int, dtype: torch.dtype = torch.bfloat16) -> None:
@@ -131,11 +158,12 @@ class PeerExchange:
         rows_bytes = aligned(world * capacity * d_model * elem)
         counts_bytes = aligned(world * experts_local * 4)
         pad_bytes = aligned(world * 4)
-        offsets = [0, rows_bytes, 2 * rows_bytes, 2 * rows_bytes + counts_bytes]
-        total = offsets[3] + pad_bytes
+        flags_bytes = aligned(world * experts_local * 4)
+        offsets = [0, rows_bytes, 2 * rows_bytes, 2 * rows_bytes + counts_bytes, 2 * rows_bytes + counts_bytes + pad_bytes]
+        total = offsets[4] + flags_bytes
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buffer, group)
-        self.buffer[offsets[2]:].zero_()  # counts and barrier pad start at zero
+        self.buffer[offsets[2]:].zero_()  # counts, barrier pad and arrival flags start at zero
         torch.cuda.synchronize(device)
         dist.barrier(group)
 
@@ -146,6 +174,7 @@ class PeerExchange:
         self.ret = view(offsets[1], world * capacity * d_model * elem, dtype).view(world * capacity, d_model)
         self.counts = view(offsets[2], world * experts_local * 4, torch.int32).view(world, experts_local)
         self.pad = view(offsets[3], world * 4, torch.int32)
+        self.flags = view(offsets[4], world * experts_local * 4, torch.int32)
         bases = [int(p) for p in self.handle.buffer_ptrs]
 
         def table(off: int) -> torch.Tensor:
@@ -153,7 +182,9 @@ class PeerExchange:
 
         self.peer_recv, self.peer_ret = table(offsets[0]), table(offsets[1])
         self.peer_counts, self.peer_pads = table(offsets[2]), table(offsets[3])
+        self.peer_flags = table(offsets[4])
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.done = torch.zeros(world * experts_local, dtype=torch.int32, device=device)  # push chunk counters
 
 
 @dataclass
@@ -173,7 +204,8 @@ class ExpertParallelMoE:
 
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
                  group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
-                 exchange: str = "nccl", fuse_return: bool = True, micro_batches: int = 1) -> None:
+                 exchange: str = "nccl", fuse_return: bool = True, micro_batches: int = 1,
+                 fuse_dispatch: bool = True) -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
         (source, destination) pair; None means T*k of the first call's batch (never overflows).
         `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
@@ -181,12 +213,16 @@ class ExpertParallelMoE:
         device-side barrier (only real rows travel; needs `capacity` up front and world size > 1).
         `fuse_return` (peer exchange only): the owner's DSD stores its rows straight into the source
         ranks' buffers from its epilogue instead of writing y and pushing it with a second kernel.
+        `fuse_dispatch` (peer exchange only): only the counts are exchanged before the owner's layout is
+        built; the rows are pushed by extra warps of the owner's SDD kernel and every SDD tile waits for
+        its own expert's rows, instead of pushing all rows and waiting for all ranks before SDD starts.
         `micro_batches` (peer exchange only): the T local tokens are cut into that many equal parts, each
         a complete step with its own exchange buffers on its own stream, ordered so that part m+1 is
         dispatched while part m is computed and part m returns while part m+1 is computed. Same result
         bit for bit; every part reads the owner's expert weights again, so it pays only where the
         owner's matmuls are tensor-bound (many tokens per expert) and the exchange is a large share."""
         self.fuse_return = fuse_return
+        self.fuse_dispatch = fuse_dispatch
         self.micro_batches = int(micro_batches)
         if self.micro_batches < 1:
             raise ValueError("micro_batches must be >= 1")
@@ -294,6 +330,9 @@ class ExpertParallelMoE:
         send_index, return_row = ops.plan(offsets, sorted_token, copy_pos, world, self.experts_local, capacity,
                                           self.status)
         mark("dispatch plan")
+        if peer is not None and self.fuse_dispatch and hasattr(ops, "sdd_dispatch"):
+            return self._forward_peer_overlapped(x, expert_weight, send_index, return_row, mark,
+                                                 (counts, offsets, sorted_token, copy_pos), peer, capacity, after_dispatch)
         if peer is not None:
             return self._forward_peer(x, expert_weight, counts, send_index, return_row, mark,
                                       (counts, offsets, sorted_token, copy_pos), peer, capacity, after_dispatch)
@@ -348,6 +387,35 @@ class ExpertParallelMoE:
         out = ops.combine(peer.ret, return_row, expert_weight)
         mark("combine")
         self.last = StepTrace(source_sort, send_index, return_row, peer.counts, slot_expert, topo)
+        return out
+
+    def _forward_peer_overlapped(self, x, expert_weight, send_index, return_row, mark, source_sort, peer, capacity,
+                                 after_dispatch) -> torch.Tensor:
+        """Steps 3-5 with both exchange legs inside the owner's matmul kernels (see the module text)."""
+        ops = self.ops
+        _, offsets, sorted_token, _ = source_sort
+        x = x.contiguous()
+        plan = ops.dispatch_plan(offsets, self.world, self.experts_local, capacity, self.rank, peer.peer_counts)
+        ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)  # counts only: nothing heavy to wait for
+        mark("dispatch all-to-all")
+        topo = ops.owner_layout(peer.counts, capacity, self.ffn_dim)
+        mark("routing")
+        h = ops.sdd_dispatch(peer, self.w1, topo, x, sorted_token, plan, self.rank, capacity)
+        if after_dispatch is not None:
+            after_dispatch()
+        mark("SDD + GELU (fused)")
+        if self.fuse_return and hasattr(ops, "dsd_push"):
+            ops.dsd_push(h, self.w2_cat, topo, peer.peer_ret, self.rank, capacity)
+            mark("DSD")
+        else:
+            y = ops.dsd(h, self.w2_cat, topo)
+            mark("DSD")
+            ops.push_rows(y, topo.copy_row, peer.peer_ret, self.rank, capacity)
+        ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)
+        mark("return all-to-all")
+        out = ops.combine(peer.ret, return_row, expert_weight)
+        mark("combine")
+        self.last = StepTrace(source_sort, send_index, return_row, peer.counts, None, topo)
         return out
 
     __call__ = forward

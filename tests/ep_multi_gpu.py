@@ -5,7 +5,8 @@ launches under torchrun (pytest does not collect this file itself). By hand:
         --master-port 29511 tests/ep_multi_gpu.py [nccl|peer|peer_unfused|peer_mb2|peer_mb4|bench] [small|full]
 
 (peer: the owner's DSD stores its rows into the source ranks' buffers from its epilogue;
-peer_unfused: DSD writes y and a second kernel pushes it; peer_mbM: the step cut into M micro-batches
+peer_unfused: DSD writes y and a second kernel pushes it; peer_nodispatch: all rows are pushed by a kernel of
+their own and every rank waits for all of them before the owner's routing; peer_mbM: the step cut into M micro-batches
 pipelined over M streams; bench: exactly what the benchmark runs at this rank count.)
 
 small: T=512 tokens per rank, D=256, F=512, E=32. Every rank builds the same global batch from a seed,
@@ -103,7 +104,8 @@ def main_full(rank: int, world: int, local: int, mode: str) -> None:
         micro_batches = int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1
         fuse = mode != "peer_unfused"
     layer = ExpertParallelMoE(w1_all[mine.start:mine.stop].cuda(), w2_all[mine.start:mine.stop].cuda(), experts,
-                              capacity=tokens * k, exchange=exchange, fuse_return=fuse, micro_batches=micro_batches)
+                              capacity=tokens * k, exchange=exchange, fuse_return=fuse, micro_batches=micro_batches,
+                              fuse_dispatch=mode != "peer_nodispatch")
 
     def batch(shift: int):
         """Rank r's tokens as the benchmark draws them (token seed r + shift, weights and Zipf order seed 0)."""
@@ -159,6 +161,7 @@ def main() -> None:
     exchange = "peer" if mode.startswith("peer") else mode
     layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
                               capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused",
+                              fuse_dispatch=mode != "peer_nodispatch",
                               micro_batches=int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1)
     mine = slice(rank * T, (rank + 1) * T)
 

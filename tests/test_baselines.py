@@ -8,7 +8,7 @@ import bench_baselines as B
 from oracle import moe as M
 from sparsebench_b200.workloads import LayerConfig, make_layer
 
-CFG = LayerConfig("baseline_check", num_tokens=300, d_model=128, ffn_dim=256, num_experts=8, routing="zipf")
+CFG = LayerConfig("baseline_check", num_tokens=300, d_model=256, ffn_dim=256, num_experts=8, routing="zipf")
 
 
 def expected_and_inputs(dtype: torch.dtype):

@@ -16,7 +16,11 @@ def test_reference_arm_prints_the_contract_keys() -> None:
     line = json.loads(proc.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["higher_is_better"] is True
     assert line["config"]["workload"] == "cpu_small" and line["n_gpus"] == 1
-    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    # "reference": the reference's own reference.py from the copy under baseline/_ref; "port": the oracle.
+    have_copy = (ROOT / "baseline" / "_ref" / "sparsebench_ref" / "reference.py").exists()
+    assert line["cpu_baseline"]["kind"] == ("reference" if have_copy else "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["steps"] == 2 and set(line["config"]) == {"workload", "tokens", "d_model", "ffn_dim", "experts", "top_k",
+                                                          "routing", "block_size"}
     assert line["e2e"] == {"value": line["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert line["value"] > 0 and line["ms_per_step"] > 0 and line["gpu_launches"] == 0
 

@@ -189,3 +189,205 @@ def test_dsd_push_into_own_memory_matches_dsd_then_push(case: str) -> None:
     torch.cuda.synchronize()
     assert torch.equal(got, want)
     assert bool((want != 7.0).any())
+
+
+# ---- dispatch overlapped with the owner's first matmul ---------------------------------------------------
+
+@pytest.mark.parametrize(("ranks", "experts_local", "capacity"), [(2, 4, 64), (8, 16, 8192), (4, 32, 300), (1, 8, 1000)])
+def test_owner_layout_from_counts_equals_routing_of_the_slots(ranks: int, experts_local: int, capacity: int) -> None:
+    # One launch from N * E_local counts must leave what slot experts + routing (k = 1) leave, bit for bit.
+    from sparsebench_b200 import _C
+
+    g = torch.Generator().manual_seed(ranks * 100 + experts_local)
+    recv_counts = torch.randint(0, max(2, 2 * capacity // experts_local), (ranks, experts_local), generator=g,
+                                dtype=torch.int32)
+    recv_counts[0, 1:] = 0            # a source with a single expert
+    recv_counts[-1] = 0               # a source that sent nothing
+    recv_counts[:, experts_local // 2] = 0  # an expert nobody uses
+    ffn_dim = 512
+    got = _C.ep_owner_layout(recv_counts.cuda(), capacity, ffn_dim)
+    slot_expert = _C.ep_slot_experts(recv_counts.cuda(), capacity)
+    want = _C.build_topology_cuda(slot_expert.view(-1, 1), experts_local, ffn_dim, 128)
+    names = ("tokens_per_expert", "padded_offsets", "row_token", "copy_row", "row_block_expert", "row_offsets", "col_indices")
+    for name, a, b in zip(names, got, want):
+        assert torch.equal(a, b), name
+    assert int(got[-1].item()) == 0
+    # And against the CPU oracle of the slot list.
+    oracle = L.device_layout(torch.from_numpy(ep_cpu_ops.slot_experts(recv_counts.numpy(), capacity)).view(-1, 1),
+                             experts_local, ffn_dim, 128)
+    for name, a in zip(names, got):
+        assert np.array_equal(a.cpu().numpy(), getattr(oracle, name)), name
+
+
+class LocalExchange:
+    """The exchange buffers of `ranks` virtual ranks, all in this GPU's memory: what PeerExchange maps across
+    GPUs, for tests that run one rank's kernels at a time (no two launches ever wait for each other)."""
+
+    def __init__(self, ranks: int, capacity: int, d_model: int, experts_local: int) -> None:
+        dev = "cuda"
+        self.recv = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=dev)
+        self.ret = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=dev)
+        self.counts = torch.zeros(ranks, ranks, experts_local, dtype=torch.int32, device=dev)
+        self.pad = torch.zeros(ranks, ranks, dtype=torch.int32, device=dev)
+        self.flags = torch.zeros(ranks, ranks * experts_local, dtype=torch.int32, device=dev)
+        self.epoch = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(ranks)]
+        self.done = [torch.zeros(ranks * experts_local, dtype=torch.int32, device=dev) for _ in range(ranks)]
+
+        def table(t: torch.Tensor) -> torch.Tensor:
+            return torch.tensor([t[r].data_ptr() for r in range(ranks)], dtype=torch.int64, device=dev)
+
+        self.peer_recv, self.peer_ret = table(self.recv), table(self.ret)
+        self.peer_counts, self.peer_pads, self.peer_flags = table(self.counts), table(self.pad), table(self.flags)
+
+    def of(self, rank: int):
+        """Rank `rank`'s view, with the attribute names of sparsebench_b200.ep.PeerExchange."""
+        import types
+
+        return types.SimpleNamespace(
+            recv=self.recv[rank], ret=self.ret[rank], counts=self.counts[rank], pad=self.pad[rank], flags=self.flags[rank],
+            epoch=self.epoch[rank], done=self.done[rank], peer_recv=self.peer_recv, peer_ret=self.peer_ret,
+            peer_counts=self.peer_counts, peer_pads=self.peer_pads, peer_flags=self.peer_flags)
+
+
+@pytest.mark.parametrize(("ranks", "capacity"), [(2, 600), (4, 40)])
+def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_every_flag(ranks: int, capacity: int) -> None:
+    from sparsebench_b200 import _C
+
+    num_tokens, num_experts, d_model = 300, 16, 256
+    experts_local = num_experts // ranks
+    g = torch.Generator().manual_seed(5)
+    old, new = LocalExchange(ranks, capacity, d_model, experts_local), LocalExchange(ranks, capacity, d_model, experts_local)
+    for rank in range(ranks):  # one virtual rank at a time
+        x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
+        idx = routing_case("zipf", num_tokens, num_experts, seed=rank).cuda()
+        counts, offsets, sorted_token, copy_pos, _ = _C.sort_copies_cuda(idx, num_experts)
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        send_index, _ = _C.ep_plan(offsets, sorted_token, copy_pos, ranks, experts_local, capacity, status)
+        _C.ep_push_counts(counts, old.peer_counts, rank, experts_local)
+        _C.ep_push_rows(x, send_index, old.peer_recv, rank, capacity)
+        view = new.of(rank)
+        view.epoch.fill_(7)
+        plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, new.peer_counts)
+        _C.ep_push_rows_flagged(x, sorted_token, plan, new.peer_recv, new.peer_flags, view.done, view.epoch, rank,
+                                experts_local, capacity)
+        torch.cuda.synchronize()
+        assert int(view.done.abs().sum().item()) == 0, "chunk counters must be left at zero"
+        pairs = ranks * experts_local
+        chunk_prefix, kept = plan[: pairs + 1].cpu(), plan[3 * (pairs + 1): 3 * (pairs + 1) + pairs].cpu()
+        assert int(kept.sum().item()) == int((send_index >= 0).sum().item())
+        assert torch.equal(chunk_prefix[1:] - chunk_prefix[:-1], torch.clamp((kept + 3) // 4, min=1).to(torch.int32))
+    assert torch.equal(new.recv, old.recv)
+    assert torch.equal(new.counts, old.counts)
+    assert bool((new.flags == 7).all()), "every (source, expert) flag at every owner carries the epoch"
+
+
+@pytest.mark.parametrize("case", ["zipf", "random", "empty_middle"])
+def test_overlapped_dispatch_single_rank_is_the_plain_layer(case: str) -> None:
+    # World size 1 with the exchange buffers in local memory: the SDD kernel pushes this rank's rows to
+    # itself and waits for its own flags. Same rows, same kernels: bit-identical to moe_forward, in both
+    # dispatch modes, eagerly and twice in a row (the second step must wait for the second epoch).
+    from sparsebench_b200 import moe_forward
+    from sparsebench_b200.ep import ExpertParallelMoE, _no_mark
+
+    g = torch.Generator().manual_seed(2)
+    num_tokens, num_experts, d_model, ffn_dim = 300, 16, 256, 512
+    w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16().cuda()
+    w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
+    layer = ExpertParallelMoE(w1, w2, num_experts)
+    capacity = num_tokens * 2
+    peer = LocalExchange(1, capacity, d_model, num_experts).of(0)
+    for step in range(2):
+        x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
+        gate = torch.rand(num_tokens, 2, generator=g).bfloat16().cuda()
+        idx = routing_case(case, num_tokens, num_experts, seed=step).cuda()
+        want = moe_forward(x, idx, gate, w1, w2)
+        for overlapped in (True, False):
+            layer.fuse_dispatch = overlapped
+            out = layer._forward_part(x, idx, gate, _no_mark, peer, capacity, None)
+            layer.check()
+            assert torch.equal(out, want), f"step {step}, overlapped={overlapped}"
+
+
+def test_two_virtual_ranks_overlapped_dispatch_matches_oracle() -> None:
+    # Two ranks' worth of data on one GPU, one rank's kernels at a time: rank 1's rows are pushed by the
+    # stand-alone push kernel first (it waits for nothing), then rank 0's SDD pushes its own rows and finds
+    # rank 1's flags already raised. Checks rank 0's SDD blocks against the oracle of the concatenated batch.
+    from sparsebench_b200 import _C
+    from sparsebench_b200.routing import DeviceTopology
+
+    ranks, num_tokens, num_experts, d_model, ffn_dim = 2, 200, 8, 256, 512
+    experts_local, capacity = num_experts // ranks, 400
+    g = torch.Generator().manual_seed(9)
+    w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16()
+    ex = LocalExchange(ranks, capacity, d_model, experts_local)
+    xs = [torch.randn(num_tokens, d_model, generator=g).bfloat16() for _ in range(ranks)]
+    idxs = [routing_case("random", num_tokens, num_experts, seed=10 + r) for r in range(ranks)]
+    plans, sorts = [], []
+    for rank in range(ranks):
+        ex.epoch[rank].fill_(3)
+        _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idxs[rank].cuda(), num_experts)
+        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts))
+        sorts.append(sorted_token)
+    x_dev = [x.cuda() for x in xs]
+    view1 = ex.of(1)
+    _C.ep_push_rows_flagged(x_dev[1], sorts[1], plans[1], ex.peer_recv, ex.peer_flags, view1.done, view1.epoch, 1,
+                            experts_local, capacity)
+    torch.cuda.synchronize()
+    view0 = ex.of(0)
+    out = _C.ep_owner_layout(view0.counts, capacity, ffn_dim)
+    topo = DeviceTopology(128, experts_local, ffn_dim // 128, *out)
+    h = _C.ep_sdd_dispatch(view0.recv, w1[:experts_local].cuda(), topo.row_token, topo.row_block_expert, topo.row_offsets,
+                           topo.col_indices.numel(), x_dev[0], sorts[0], plans[0], ex.peer_recv, ex.peer_flags, view0.flags,
+                           view0.done, view0.epoch, 0, capacity)
+    torch.cuda.synchronize()
+    # Oracle: rank 0 owns experts [0, experts_local); its rows are the global batch's rows of those experts.
+    x_all, idx_all = torch.cat(xs), torch.cat(idxs)
+    whole = L.build_topology(idx_all, num_experts, ffn_dim, 128)
+    blocks = M.sdd_blocks(x_all.float(), w1.float(), whole, gelu=True)
+    rows_owned = int(whole.padded_offsets[experts_local])
+    live = rows_owned // 128 * (ffn_dim // 128)
+    counts = whole.tokens_per_expert[:experts_local]
+    got, want = h[:live].float().cpu().view(-1, ffn_dim // 128, 128, 128), blocks[:live].view(-1, ffn_dim // 128, 128, 128)
+    for e in range(experts_local):  # compare each expert's real rows (padding groups of 32 are not stored)
+        first_rb = int(whole.padded_offsets[e]) // 128
+        for j in range(int(counts[e])):
+            rb, r = first_rb + j // 128, j % 128
+            torch.testing.assert_close(got[rb, :, r], want[rb, :, r], rtol=1.6e-2, atol=1.6e-2)
+
+
+def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers() -> None:
+    # Failure detection without a fault: two virtual ranks, rank 1 never pushes, so its arrival flags are
+    # never raised. Rank 0's SDD waits its bounded second per tile role, records SB_DEV_TIMEOUT_DISPATCH in
+    # the status word and winds down; the context stays usable.
+    import time
+
+    from sparsebench_b200 import _C
+    from sparsebench_b200.routing import DeviceTopology
+
+    ranks, num_tokens, num_experts, d_model, ffn_dim, capacity = 2, 64, 4, 256, 256, 128
+    experts_local = num_experts // ranks
+    g = torch.Generator().manual_seed(1)
+    ex = LocalExchange(ranks, capacity, d_model, experts_local)
+    x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
+    w1 = torch.randn(experts_local, d_model, ffn_dim, generator=g).bfloat16().cuda()
+    idx = routing_case("random", num_tokens, num_experts, seed=0).cuda()
+    _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx, num_experts)
+    view = ex.of(0)
+    view.epoch.fill_(1)
+    plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, 0, ex.peer_counts)
+    view.counts[1] = view.counts[0]  # pretend rank 1 announced rows that never come
+    topo = DeviceTopology(128, experts_local, ffn_dim // 128, *_C.ep_owner_layout(view.counts, capacity, ffn_dim))
+    status = _C.device_status(torch.device("cuda", torch.cuda.current_device()))
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    _C.ep_sdd_dispatch(view.recv, w1, topo.row_token, topo.row_block_expert, topo.row_offsets, topo.col_indices.numel(),
+                       x, sorted_token, plan, ex.peer_recv, ex.peer_flags, view.flags, view.done, view.epoch, 0, capacity)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - started
+    word = int(status.item())
+    status.zero_()
+    assert word & 8, f"SB_DEV_TIMEOUT_DISPATCH expected in the status word, got {word}"
+    assert 0.5 < waited < 20.0
+    assert bool((ex.flags[0, :experts_local] == 1).all()) and bool((ex.flags[0, experts_local:] == 0).all())
+    # Still healthy: the plain kernel runs.
+    assert int(_C.arch_probe(4)[0].item()) == 1000

@@ -48,7 +48,7 @@ def test_benchmark_shape_matches_oracle_on_every_rank(world: int) -> None:
         assert f"rank {rank}/{world}: expert-parallel parity ok" in text, text[-3000:]
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer_unfused", "peer_mb2"])
+@pytest.mark.parametrize("mode", ["nccl", "peer_unfused", "peer_nodispatch", "peer_mb2"])
 def test_other_exchange_modes_small_shape(mode: str) -> None:
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
