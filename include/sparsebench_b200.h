@@ -137,11 +137,15 @@ int sb_route_static_scratch(const void* expert_idx, int idx_is_i64, int64_t n_co
  * padding rows sit at the end of each row block, as sb_route writes them, a group of 32 rows that is
  * all padding is not stored (those rows of the blocks stay unwritten instead of 0), which saves
  * their share of the H traffic. Pair it with sb_dsd's row_token argument.
+ * padded_offsets (no reference counterpart; NULL = never): sb_route's [num_experts + 1] array for this
+ * layout. With it, layouts whose experts have several row blocks each (worst case >= 4 per expert, at
+ * most 128 experts) run two row blocks of one expert per tile on a pair of thread blocks (tcgen05
+ * cta_group::2), each of which loads only half of every weight tile. Same results.
  */
 int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
            const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
            int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int skip_padding_rows,
-           int32_t* dev_status, sb_stream_t stream);
+           const int32_t* padded_offsets, int32_t* dev_status, sb_stream_t stream);
 
 /*
  * DSD: y[rb*bs + r][:] = sum over p in [row_offsets[rb], row_offsets[rb+1]) of
@@ -155,10 +159,15 @@ int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_
  * [num_row_blocks * block_size] row -> token table with padding rows (< 0) at the end of each row
  * block. When given, a group of 32 rows that is all padding is neither read from h_blocks nor
  * written to y (those rows of y stay unwritten).
+ * padded_offsets / num_experts (no reference counterpart; NULL / 0 = never): only for a layout made by
+ * sb_route, where all row blocks of an expert have the same column blocks; as for sb_sdd, such a layout
+ * with several row blocks per expert then runs on pairs of thread blocks. A general BSR matrix must
+ * pass NULL.
  */
 int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
            const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks, int32_t block_size,
-           int zero_dead_rows, const int32_t* row_token, void* y, int32_t* dev_status, sb_stream_t stream);
+           int zero_dead_rows, const int32_t* row_token, void* y, const int32_t* padded_offsets, int32_t num_experts,
+           int32_t* dev_status, sb_stream_t stream);
 
 /*
  * Combine: out[t][:] = bf16( sum_j float(y[copy_row[t*k+j]][:]) * float(gate[t][j]) ), products and
@@ -179,6 +188,22 @@ int sb_combine(const void* y, const int32_t* copy_row, const void* gate, int gat
  */
 int sb_router_topk(const void* logits, int logits_dtype, int64_t num_tokens, int32_t num_experts, int32_t k,
                    void* expert_idx, int idx_is_i64, void* expert_weight, sb_stream_t stream);
+
+/*
+ * Router and routing in ONE launch: what sb_router_topk followed by sb_route leaves (expert_idx int64
+ * [T, k], expert_weight in the logits' type, and the eight layout arrays of sb_route), computed by one
+ * thread-block cluster that never writes the ids out before sorting them. Replaces the host-side
+ * torch.topk + softmax of sparsebench/reference.py:19-29 AND sparsebench::build_topology_cuda
+ * (csrc/routing.cu:197-281) together. Available where sb_route_from_logits_fused(T, k, E) returns 1
+ * (k in {1, 2, 4, 8}, E <= 256, T*k <= 32768); elsewhere it returns SB_ERR_UNSUPPORTED and the two
+ * separate calls give the same result.
+ */
+int sb_route_from_logits_fused(int64_t num_tokens, int32_t k, int32_t num_experts);
+int sb_route_from_logits(const void* logits, int logits_dtype, int64_t num_tokens, int32_t k, int32_t num_experts,
+                         int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int64_t* expert_idx,
+                         void* expert_weight, int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* row_token,
+                         int32_t* copy_row, int32_t* row_block_expert, int32_t* row_offsets, int32_t* col_indices,
+                         int32_t* error, sb_stream_t stream);
 
 /*
  * The layer on a flat assignment list: copy c sends token token_of_copy[c] to expert

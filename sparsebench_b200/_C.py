@@ -94,11 +94,12 @@ def _check_index(t: torch.Tensor, name: str) -> None:
 
 def sdd_cuda(x: torch.Tensor, w1: torch.Tensor, row_token: torch.Tensor, row_block_expert: torch.Tensor,
              row_offsets: torch.Tensor, num_nnz: int, apply_gelu: bool,
-             skip_padding_rows: bool = False) -> torch.Tensor:
+             skip_padding_rows: bool = False, padded_offsets: torch.Tensor | None = None) -> torch.Tensor:
     """Blocks [num_nnz, 128, 128] = (gelu)(x[row_token] @ w1[expert]) on the layout's blocks.
     Reference: csrc/sdd.cu:123-170. Blocks of dead row blocks are left unwritten; with
     skip_padding_rows so are groups of 32 rows that are all padding (padding at the end of each row
-    block, as routing lays it out) instead of coming out 0."""
+    block, as routing lays it out) instead of coming out 0. padded_offsets (routing's [E + 1] array):
+    lets layouts with several row blocks per expert run two row blocks per tile on pairs of thread blocks."""
     lib = _lib.load()
     _check(x.is_cuda and w1.is_cuda and x.device == w1.device, "x and w1 must be on the same GPU (CUDA tensors)")
     _check(x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16, "x and w1 must be bfloat16")
@@ -108,6 +109,9 @@ def sdd_cuda(x: torch.Tensor, w1: torch.Tensor, row_token: torch.Tensor, row_blo
     _check_index(row_token, "row_token")
     _check_index(row_block_expert, "row_block_expert")
     _check_index(row_offsets, "row_offsets")
+    if padded_offsets is not None:
+        _check_index(padded_offsets, "padded_offsets")
+        _check(padded_offsets.numel() == w1.shape[0] + 1, "padded_offsets must have E + 1 entries")
     d_model, ffn_dim = x.shape[1], w1.shape[2]
     num_row_blocks = row_offsets.numel() - 1
     _check(d_model > 0 and d_model % 64 == 0, f"sdd needs D ({d_model}) to be a multiple of 64")
@@ -124,6 +128,7 @@ def sdd_cuda(x: torch.Tensor, w1: torch.Tensor, row_token: torch.Tensor, row_blo
             _lib.check(lib.sb_sdd(_ptr(x), _ptr(w1), _ptr(row_token), _ptr(row_block_expert), _ptr(row_offsets),
                                   _ptr(out), x.shape[0], d_model, ffn_dim, w1.shape[0], num_row_blocks,
                                   int(bool(apply_gelu)), int(bool(skip_padding_rows)),
+                                  _ptr(padded_offsets) if padded_offsets is not None else None,
                                   _ptr(device_status(x.device)), _stream()))
     return out
 
@@ -133,13 +138,16 @@ _DSD_ZERO_DEAD_ROWS = {1, 2, 21, 3, 31}
 
 
 def dsd_cuda(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, col_indices: torch.Tensor,
-             version: int, row_token: torch.Tensor | None = None) -> torch.Tensor:
+             version: int, row_token: torch.Tensor | None = None,
+             padded_offsets: torch.Tensor | None = None) -> torch.Tensor:
     """out [num_row_blocks*bs, D] = BSR(blocks, row_offsets, col_indices) @ w.
     Reference: csrc/dsd.cpp:27-80. `version` keeps the reference's meaning for what is observable:
     versions 1, 2, 21, 3, 31 zero the rows of row blocks without blocks, 4, 41 and 5 leave them
     unwritten, 5 insists on block size 128 and D % 256 == 0; one tcgen05 kernel serves them all.
     With row_token (the layout's row -> token table, padding at the end of each row block), groups of
-    32 rows that are all padding are neither read nor written."""
+    32 rows that are all padding are neither read nor written. padded_offsets (routing's [E + 1] array,
+    only for a layout routing made): lets layouts with several row blocks per expert run on pairs of
+    thread blocks."""
     lib = _lib.load()
     _check(blocks.is_cuda and w.is_cuda, "blocks and w must be CUDA tensors")
     _check(blocks.device == w.device and row_offsets.device == w.device and col_indices.device == w.device,
@@ -163,6 +171,8 @@ def dsd_cuda(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, c
     if version == 5:
         _check(bs == 128 and d_model % 256 == 0,
                f"dsd v5 needs block size 128 and D a multiple of 256, got block size {bs}, D {d_model}")
+    if padded_offsets is not None:
+        _check_index(padded_offsets, "padded_offsets")
     if row_token is not None:
         _check_index(row_token, "row_token")
         _check(row_token.device == w.device and row_token.numel() == num_row_blocks * bs,
@@ -174,6 +184,8 @@ def dsd_cuda(blocks: torch.Tensor, w: torch.Tensor, row_offsets: torch.Tensor, c
             _lib.check(lib.sb_dsd(_ptr(blocks), blocks.shape[0], _ptr(w), w.shape[0], d_model, _ptr(row_offsets),
                                   _ptr(col_indices), num_row_blocks, bs, int(version in _DSD_ZERO_DEAD_ROWS),
                                   _ptr(row_token) if row_token is not None else None, _ptr(out),
+                                  _ptr(padded_offsets) if padded_offsets is not None else None,
+                                  padded_offsets.numel() - 1 if padded_offsets is not None else 0,
                                   _ptr(device_status(w.device)), _stream()))
     return out
 
@@ -216,6 +228,34 @@ def router_topk_cuda(logits: torch.Tensor, k: int, index_dtype: torch.dtype = to
             _lib.check(lib.sb_router_topk(_ptr(logits), int(logits.dtype == torch.float32), num_tokens, num_experts, k,
                                           _ptr(idx), int(index_dtype == torch.int64), _ptr(weight), _stream()))
     return idx, weight
+
+
+def route_from_logits_cuda(logits: torch.Tensor, k: int, ffn_dim: int, block_size: int):
+    """(expert_idx [T, k] int64, expert_weight [T, k], the eight arrays of build_topology_cuda) from router
+    logits [T, E]. One kernel launch where the fused form applies (k in {1, 2, 4, 8}, E <= 256, T*k <= 32768),
+    otherwise router_topk_cuda followed by build_topology_cuda: same results either way."""
+    lib = _lib.load()
+    _check(logits.is_cuda and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous [T, E] CUDA tensor")
+    _check(logits.dtype in (torch.bfloat16, torch.float32), "logits must be bfloat16 or float32")
+    num_tokens, num_experts = logits.shape
+    _check(0 < k <= num_experts, f"need [T, E] logits with 0 < k <= E, got {tuple(logits.shape)} and k={k}")
+    if num_tokens == 0 or not lib.sb_route_from_logits_fused(num_tokens, k, num_experts):
+        idx, weight = router_topk_cuda(logits, k)
+        return idx, weight, build_topology_cuda(idx, num_experts, ffn_dim, block_size)
+    n = num_tokens * k
+    max_rb, max_rows, ffn_blocks = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+    _lib.check(lib.sb_route_sizes(n, num_experts, ffn_dim, block_size, ctypes.byref(max_rb), ctypes.byref(max_rows),
+                                  ctypes.byref(ffn_blocks)))
+    max_rb, max_rows, ffn_blocks = max_rb.value, max_rows.value, ffn_blocks.value
+    with torch.cuda.device(logits.device):
+        idx = torch.empty((num_tokens, k), dtype=torch.int64, device=logits.device)
+        weight = torch.empty((num_tokens, k), dtype=logits.dtype, device=logits.device)
+        sizes = [num_experts, num_experts + 1, max_rows, n, max_rb, max_rb + 1, max_rb * ffn_blocks, 1]
+        parts = list(torch.split(torch.empty(sum(sizes), dtype=torch.int32, device=logits.device), sizes))
+        _lib.check(lib.sb_route_from_logits(_ptr(logits), int(logits.dtype == torch.float32), num_tokens, k, num_experts,
+                                            ffn_blocks, block_size, max_rb, _ptr(idx), _ptr(weight),
+                                            *(_ptr(t) for t in parts), _stream()))
+    return idx, weight, parts
 
 
 # ---- the layer on a flat assignment list (PyTorch ops in the reference, sparsebench/moe.py:59-91) ---

@@ -6,8 +6,8 @@ package does not load the CUDA library; the first operator call does, and fails 
 missing. There is no CPU or PyTorch fallback.
 """
 
-from sparsebench_b200.moe import moe_forward, moe_forward_assigned
-from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route, route_device
+from sparsebench_b200.moe import moe_forward, moe_forward_assigned, moe_forward_from_logits
+from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route, route_and_layout, route_device
 from sparsebench_b200.spmm import combine, dsd, sdd
 from sparsebench_b200.topology import Topology
 
@@ -19,7 +19,9 @@ __all__ = [
     "dsd",
     "moe_forward",
     "moe_forward_assigned",
+    "moe_forward_from_logits",
     "route",
+    "route_and_layout",
     "route_device",
     "sdd",
 ]

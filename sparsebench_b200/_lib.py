@@ -28,10 +28,13 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                          _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_route_static_scratch": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
                                         _P, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, c_int, _P, _P]),
-    "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P, _P]),
+    "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, c_int, _P, _P, _P]),
+    "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P, c_int32, _P, _P]),
     "sb_combine": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int32, c_int32, _P]),
     "sb_router_topk": (c_int, [_P, c_int, c_int64, c_int32, c_int32, _P, c_int, _P, _P]),
+    "sb_route_from_logits_fused": (c_int, [c_int64, c_int32, c_int32]),
+    "sb_route_from_logits": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, _P, _P,
+                                     _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_remap_rows": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, c_int64, _P]),
     "sb_combine_assigned": (c_int, [_P, _P, _P, c_int, _P, c_int, _P, _P, c_int64, c_int64, c_int32, _P]),
     "sb_ep_plan": (c_int, [_P, _P, _P, c_int64, c_int32, c_int32, c_int32, _P, _P, _P, _P]),

@@ -2,7 +2,7 @@
 // rules follow the reference's sparsebench::dsd_cuda (csrc/dsd.cpp:27-80); the kernel is
 // bsr_gemm_kernel<kDsd, 256> when D is a multiple of 256 and the 128-wide instance otherwise.
 
-#include "bsr_gemm.cuh"
+#include "bsr_gemm_pair.cuh"
 
 namespace sb {
 namespace {
@@ -16,8 +16,8 @@ struct PeerReturn {
 
 int dsd_launch(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
                const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks, int32_t block_size,
-               int zero_dead_rows, const int32_t* row_token, void* y, const PeerReturn& peer, int32_t* dev_status,
-               sb_stream_t stream) {
+               int zero_dead_rows, const int32_t* row_token, void* y, const PeerReturn& peer,
+               const int32_t* padded_offsets, int32_t num_experts, int32_t* dev_status, sb_stream_t stream) {
   if (block_size != 64 && block_size != 128)
     return fail(SB_ERR_INVALID_ARGUMENT, "block size must be 64 or 128, got %d", block_size);
   if (d_model <= 0 || d_model % 128 != 0)
@@ -74,6 +74,14 @@ int dsd_launch(const void* h_blocks, int64_t num_blocks, const void* w, int64_t 
   params.row_token = row_token;
   params.skip_padding = row_token != nullptr ? 1 : 0;
   params.d_model = d_model;
+  if (d_model % 256 == 0 && block_size == 128 && !zero_dead_rows &&
+      use_pair_kernel(padded_offsets, num_row_blocks, num_experts)) {
+    // Layout made by the routing kernel (every row block of an expert has the same column blocks): two row
+    // blocks of one expert per tile, on a pair of thread blocks.
+    params.num_slices = d_model / 256;
+    return launch_gemm_pair<GemmOp::kDsd>(map_a, map_a_rows32, map_b, map_out, params, padded_offsets, num_experts,
+                                          as_stream(stream), "dsd");
+  }
   if (d_model % 256 == 0) {
     params.num_slices = d_model / 256;
     return launch_gemm<GemmOp::kDsd, 256>(map_a, map_a_rows32, map_b, map_out, params, as_stream(stream), "dsd");
@@ -88,10 +96,12 @@ int dsd_launch(const void* h_blocks, int64_t num_blocks, const void* w, int64_t 
 extern "C" int sb_dsd(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
                       const int32_t* row_offsets, const int32_t* col_indices, int32_t num_row_blocks,
                       int32_t block_size, int zero_dead_rows, const int32_t* row_token, void* y,
-                      int32_t* dev_status, sb_stream_t stream) {
+                      const int32_t* padded_offsets, int32_t num_experts, int32_t* dev_status, sb_stream_t stream) {
   sb::clear_error();
+  if (padded_offsets != nullptr && num_experts <= 0)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "dsd: padded_offsets given without the number of experts");
   return sb::dsd_launch(h_blocks, num_blocks, w, w_rows, d_model, row_offsets, col_indices, num_row_blocks, block_size,
-                        zero_dead_rows, row_token, y, sb::PeerReturn{}, dev_status, stream);
+                        zero_dead_rows, row_token, y, sb::PeerReturn{}, padded_offsets, num_experts, dev_status, stream);
 }
 
 extern "C" int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int64_t w_rows, int32_t d_model,
@@ -108,5 +118,5 @@ extern "C" int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const vo
   peer.my_rank = my_rank;
   peer.capacity = capacity;
   return dsd_launch(h_blocks, num_blocks, w, w_rows, d_model, row_offsets, col_indices, num_row_blocks, 128, 0, row_slot,
-                    nullptr, peer, dev_status, stream);
+                    nullptr, peer, nullptr, 0, dev_status, stream);
 }

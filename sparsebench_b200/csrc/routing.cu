@@ -24,6 +24,7 @@
 // is written exactly once, by the scatter or by the fill), so no memset is needed.
 
 #include <cooperative_groups.h>
+#include <cuda_bf16.h>
 
 #include <atomic>
 
@@ -78,6 +79,105 @@ __device__ __forceinline__ unsigned same_expert_lanes(int32_t e, bool valid, int
   }
   return valid ? peers : 0u;
 }
+
+// Where a warp's run of expert ids comes from. IndexSource reads the caller's expert_idx. LogitSource is the
+// router itself: it reads the tokens' router logits, picks the k largest per token (ties to the lower id, NaN
+// above everything, as torch.topk orders them), writes expert_idx and the softmax of the k picked logits
+// (reference: sparsebench/reference.py:19-29) and hands the ids on in registers, so that logits -> layout is ONE
+// launch and the ids never make a round trip through memory before they are sorted.
+template <typename index_t>
+struct IndexSource {
+  const index_t* expert_idx;
+  int32_t num_experts;
+  template <int kIters>
+  __device__ __forceinline__ bool load(int64_t begin, int64_t end, int lane, int32_t (&ids)[kIters]) const {
+    return load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
+  }
+};
+
+constexpr int kLogitsPerLane = 8;  // fused router: up to 256 experts
+constexpr int kRouterMaxK = 8;
+
+__device__ __forceinline__ bool logit_ranks_before(float a, int32_t ia, float b, int32_t ib) {
+  const bool an = a != a, bn = b != b;
+  if (an != bn) return an;
+  if (!an && a != b) return a > b;
+  return ia < ib;
+}
+
+template <typename logit_t>
+struct LogitSource {
+  const logit_t* logits;   // [T, E]
+  int64_t* expert_idx;     // [T, k] out
+  logit_t* expert_weight;  // [T, k] out
+  int32_t num_experts;
+  int32_t k;               // a power of two <= 8, so that a 32-copy step holds whole tokens
+
+  static __device__ __forceinline__ float to_float(float v) { return v; }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+  template <int kIters>
+  __device__ __forceinline__ bool load(int64_t begin, int64_t end, int lane, int32_t (&ids)[kIters]) const {
+    const int tokens_per_step = 32 / k;
+#pragma unroll
+    for (int it = 0; it < kIters; ++it) {
+      ids[it] = -1;
+      const int64_t step_begin = begin + it * 32;
+      for (int j = 0; j < tokens_per_step; ++j) {
+        const int64_t first_copy = step_begin + static_cast<int64_t>(j) * k;
+        if (first_copy >= end) break;  // uniform across the warp
+        const int64_t t = first_copy / k;
+        const logit_t* row = logits + t * num_experts;
+        float v[kLogitsPerLane];
+#pragma unroll
+        for (int q = 0; q < kLogitsPerLane; ++q) {
+          const int e = lane + 32 * q;
+          v[q] = e < num_experts ? to_float(__ldg(row + e)) : 0.0f;
+        }
+        uint32_t retired = 0;
+        float top = 0.0f, mine = 0.0f, denom = 0.0f;
+        int32_t mine_id = 0;
+        for (int r = 0; r < k; ++r) {
+          float best = -INFINITY;
+          int32_t best_id = INT32_MAX;
+#pragma unroll
+          for (int q = 0; q < kLogitsPerLane; ++q) {
+            const int32_t e = lane + 32 * q;
+            if (e < num_experts && !((retired >> q) & 1u) && logit_ranks_before(v[q], e, best, best_id)) {
+              best = v[q];
+              best_id = e;
+            }
+          }
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) {
+            const float other = __shfl_xor_sync(kFullMask, best, d);
+            const int32_t other_id = __shfl_xor_sync(kFullMask, best_id, d);
+            if (logit_ranks_before(other, other_id, best, best_id)) {
+              best = other;
+              best_id = other_id;
+            }
+          }
+          if ((best_id & 31) == lane) retired |= 1u << (best_id >> 5);
+          if (r == 0) top = best;
+          denom += __expf(best - top);
+          if (lane == j * k + r) {  // the lane that carries this copy through the sort
+            ids[it] = best_id;
+            mine = best;
+            mine_id = best_id;
+          }
+        }
+        if (lane >= j * k && lane < (j + 1) * k) {
+          const int64_t c = first_copy + (lane - j * k);
+          expert_idx[c] = mine_id;
+          store(expert_weight + c, __expf(mine - top) / denom);
+        }
+      }
+    }
+    return false;
+  }
+};
 
 // One warp walks its run 32 copies per step, in copy order, and adds it to its private counters.
 // For every copy it also returns pos = the number of copies of the same expert that come earlier in
@@ -212,9 +312,9 @@ __device__ void fill_layout(const int32_t* offsets, const int32_t* counts, int32
 // and the scattered row_token stores are spread over as many SMs as the cluster has blocks.
 // Shared memory per block: counters[32][E+1] | cta_counts[E] | offsets[E+1] | counts[E] | cta_base[E]
 //                          | warp_sums[32] | bad[1].   (E+1: conflict-free column walks.)
-template <typename index_t, int kIters>
+template <typename Source, int kIters>
 __global__ void __launch_bounds__(kClusterThreads, 1)
-route_cluster_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t k, int32_t num_experts, int32_t id_bits,
+route_cluster_kernel(const Source source, int32_t n, int32_t k, int32_t num_experts, int32_t id_bits,
                      int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
                      int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
                      int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
@@ -240,7 +340,7 @@ route_cluster_kernel(const index_t* __restrict__ expert_idx, int32_t n, int32_t 
   const int64_t begin = min(static_cast<int64_t>(n), (static_cast<int64_t>(cta) * kWarps + warp) * run);
   const int64_t end = min(static_cast<int64_t>(n), begin + run);
   int32_t ids[kIters];
-  const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
+  const bool bad = source.template load<kIters>(begin, end, lane, ids);
   for (int i = threadIdx.x; i < kWarps * stride; i += kClusterThreads) counters[i] = 0;
   __syncthreads();
   int32_t pos[kIters];
@@ -523,13 +623,13 @@ int32_t id_bits_for(int32_t num_experts) {
   return bits;
 }
 
-template <typename index_t, int kIters>
-int launch_cluster(int device, int blocks, size_t smem, cudaStream_t stream, const index_t* expert_idx, int32_t n,
+template <typename Source, int kIters>
+int launch_cluster(int device, int blocks, size_t smem, cudaStream_t stream, const Source& source, int32_t n,
                    int32_t k, int32_t num_experts, int32_t id_bits, int32_t ffn_blocks, int32_t block_size,
                    int32_t max_row_blocks, int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* copy_row,
                    LayoutOut layout, int32_t* error) {
   static std::atomic<bool> attr_done[kMaxDevices] = {};  // a lost race only repeats the same attribute call
-  auto kernel = route_cluster_kernel<index_t, kIters>;
+  auto kernel = route_cluster_kernel<Source, kIters>;
   if (!attr_done[device].load(std::memory_order_acquire)) {
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(cluster_smem_bytes(kMaxExperts)));
@@ -548,7 +648,7 @@ int launch_cluster(int device, int blocks, size_t smem, cudaStream_t stream, con
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, expert_idx, n, k, num_experts, id_bits, ffn_blocks,
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, source, n, k, num_experts, id_bits, ffn_blocks,
                                              block_size, max_row_blocks, tokens_per_expert, padded_offsets, copy_row,
                                              layout, error);
   if (err != cudaSuccess) return fail(SB_ERR_CUDA, "routing (cluster): %s", cudaGetErrorString(err));
@@ -571,10 +671,11 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
     const int64_t steps = (n + static_cast<int64_t>(blocks) * kClusterThreads - 1) / (static_cast<int64_t>(blocks) * kClusterThreads);
     const size_t smem = cluster_smem_bytes(num_experts);
     const int32_t n32 = static_cast<int32_t>(n);
+    const IndexSource<index_t> source{expert_idx, num_experts};
 #define SB_ROUTE_CLUSTER(ITERS)                                                                                     \
-  return launch_cluster<index_t, ITERS>(device, blocks, smem, stream, expert_idx, n32, k, num_experts, id_bits,      \
-                                        ffn_blocks, block_size, max_row_blocks, tokens_per_expert, padded_offsets,  \
-                                        copy_row, layout, error)
+  return launch_cluster<IndexSource<index_t>, ITERS>(device, blocks, smem, stream, source, n32, k, num_experts,      \
+                                                     id_bits, ffn_blocks, block_size, max_row_blocks,                \
+                                                     tokens_per_expert, padded_offsets, copy_row, layout, error)
     if (steps <= 1) SB_ROUTE_CLUSTER(1);
     if (steps <= 4) SB_ROUTE_CLUSTER(4);
     if (steps <= 16) SB_ROUTE_CLUSTER(16);
@@ -606,6 +707,38 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
           expert_idx, n, k, num_experts, id_bits, ffn_blocks, block_size, max_row_blocks,
           static_cast<int32_t>(num_chunks), chunk_counts, tokens_per_expert, padded_offsets, copy_row, layout);
   return check_launch("routing (scatter + layout)");
+}
+
+// Router + routing in one cluster launch. Only where a 32-copy step holds whole tokens (k a power of two),
+// a lane holds a token's logits in 8 registers (E <= 256) and the runs stay short (T*k <= 32768).
+constexpr int64_t kFusedRouterMaxCopies = static_cast<int64_t>(kMaxClusterBlocks) * kClusterThreads * 4;
+
+bool fused_router_fits(int64_t n_copies, int32_t k, int32_t num_experts) {
+  return n_copies <= kFusedRouterMaxCopies && num_experts <= 32 * kLogitsPerLane && k >= 1 && k <= kRouterMaxK &&
+         (k & (k - 1)) == 0;
+}
+
+template <typename logit_t>
+int launch_route_logits(const logit_t* logits, int64_t num_tokens, int32_t k, int32_t num_experts, int32_t ffn_blocks,
+                        int32_t block_size, int32_t max_row_blocks, int64_t* expert_idx, logit_t* expert_weight,
+                        int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* copy_row, const LayoutOut& layout,
+                        int32_t* error, cudaStream_t stream) {
+  int device = 0;
+  if (current_device_info(&device) == nullptr) return SB_ERR_CUDA;
+  const int64_t n = num_tokens * k;
+  int blocks = static_cast<int>((n + kClusterThreads - 1) / kClusterThreads);
+  if (blocks > kMaxClusterBlocks) blocks = kMaxClusterBlocks;
+  const int64_t steps = (n + static_cast<int64_t>(blocks) * kClusterThreads - 1) / (static_cast<int64_t>(blocks) * kClusterThreads);
+  const LogitSource<logit_t> source{logits, expert_idx, expert_weight, num_experts, k};
+  const size_t smem = cluster_smem_bytes(num_experts);
+  const int32_t id_bits = id_bits_for(num_experts);
+  if (steps <= 1)
+    return launch_cluster<LogitSource<logit_t>, 1>(device, blocks, smem, stream, source, static_cast<int32_t>(n), k,
+                                                   num_experts, id_bits, ffn_blocks, block_size, max_row_blocks,
+                                                   tokens_per_expert, padded_offsets, copy_row, layout, error);
+  return launch_cluster<LogitSource<logit_t>, 4>(device, blocks, smem, stream, source, static_cast<int32_t>(n), k,
+                                                 num_experts, id_bits, ffn_blocks, block_size, max_row_blocks,
+                                                 tokens_per_expert, padded_offsets, copy_row, layout, error);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -698,6 +831,48 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
                             max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
   return sb::launch_route(static_cast<const int32_t*>(expert_idx), n_copies, k, num_experts, ffn_blocks, block_size,
                           max_row_blocks, tokens_per_expert, padded_offsets, copy_row, layout, error, workspace, s);
+}
+
+int sb_route_from_logits_fused(int64_t num_tokens, int32_t k, int32_t num_experts) {
+  return sb::fused_router_fits(num_tokens * k, k, num_experts) ? 1 : 0;
+}
+
+int sb_route_from_logits(const void* logits, int logits_dtype, int64_t num_tokens, int32_t k, int32_t num_experts,
+                         int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int64_t* expert_idx,
+                         void* expert_weight, int32_t* tokens_per_expert, int32_t* padded_offsets, int32_t* row_token,
+                         int32_t* copy_row, int32_t* row_block_expert, int32_t* row_offsets, int32_t* col_indices,
+                         int32_t* error, sb_stream_t stream) {
+  sb::clear_error();
+  if (!logits || !expert_idx || !expert_weight)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "route_from_logits: NULL buffer");
+  if (logits_dtype != 0 && logits_dtype != 1)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "route_from_logits: logits_dtype must be 0 (bf16) or 1 (fp32)");
+  if (num_tokens <= 0 || k <= 0 || k > num_experts)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "route_from_logits: need [T, E] logits with 0 < k <= E");
+  if (!sb::fused_router_fits(num_tokens * k, k, num_experts))
+    return sb::fail(SB_ERR_UNSUPPORTED,
+                    "route_from_logits: the one-launch form needs k in {1, 2, 4, 8}, E <= %d and T*k <= %lld; "
+                    "use sb_router_topk followed by sb_route",
+                    32 * sb::kLogitsPerLane, (long long)sb::kFusedRouterMaxCopies);
+  int64_t want_rb = 0;
+  if (int rc = sb_route_sizes(num_tokens * k, num_experts, static_cast<int64_t>(ffn_blocks) * block_size, block_size,
+                              &want_rb, nullptr, nullptr))
+    return rc;
+  if (ffn_blocks <= 0 || want_rb != max_row_blocks)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "route_from_logits: max_row_blocks is %d, worst case needs %lld",
+                    max_row_blocks, (long long)want_rb);
+  if (!tokens_per_expert || !padded_offsets || !row_token || !copy_row || !row_block_expert || !row_offsets ||
+      !col_indices || !error)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "route_from_logits: NULL buffer");
+  const sb::LayoutOut layout{row_token, row_block_expert, row_offsets, col_indices};
+  const cudaStream_t s = sb::as_stream(stream);
+  if (logits_dtype == 0)
+    return sb::launch_route_logits(static_cast<const __nv_bfloat16*>(logits), num_tokens, k, num_experts, ffn_blocks,
+                                   block_size, max_row_blocks, expert_idx, static_cast<__nv_bfloat16*>(expert_weight),
+                                   tokens_per_expert, padded_offsets, copy_row, layout, error, s);
+  return sb::launch_route_logits(static_cast<const float*>(logits), num_tokens, k, num_experts, ffn_blocks, block_size,
+                                 max_row_blocks, expert_idx, static_cast<float*>(expert_weight), tokens_per_expert,
+                                 padded_offsets, copy_row, layout, error, s);
 }
 
 int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,

@@ -2,7 +2,9 @@
 // the block-sparse (BSR) block list. Argument rules follow the reference host function
 // sparsebench::sdd_cuda (csrc/sdd.cu:123-170); the kernel is bsr_gemm_kernel<kSdd, 256>.
 
-#include "bsr_gemm.cuh"
+#include <cstdlib>
+
+#include "bsr_gemm_pair.cuh"
 
 namespace sb {
 namespace {
@@ -12,7 +14,7 @@ namespace {
 int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
                const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
                int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int skip_padding_rows,
-               const DispatchParams* dispatch, int32_t* dev_status, sb_stream_t stream) {
+               const int32_t* padded_offsets, const DispatchParams* dispatch, int32_t* dev_status, sb_stream_t stream) {
   if (!x || !w1 || !row_token || !row_block_expert || !row_offsets)
     return fail(SB_ERR_INVALID_ARGUMENT, "sdd: NULL buffer");
   if (num_tokens <= 0 || num_experts <= 0 || num_row_blocks < 0)
@@ -59,6 +61,11 @@ int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const in
   // so that a W1 tile is read from HBM once per band instead of once per wave (measured on the
   // Mixtral-like shape: 1027 -> 861 us; shapes with ~2 row blocks per expert lose 3-5 % and stay plain).
   params.raster_rows = num_row_blocks >= 4 * num_experts ? 8 : 1;
+  if (dispatch == nullptr && use_pair_kernel(padded_offsets, num_row_blocks, num_experts)) {
+    params.raster_rows = 4;  // bands of 4 pairs = 8 row blocks
+    return launch_gemm_pair<GemmOp::kSdd>(map_a, map_a, map_b, map_out, params, padded_offsets, num_experts,
+                                          as_stream(stream), "sdd");
+  }
   if (dispatch != nullptr) {
     params.dispatch = *dispatch;
     return launch_gemm<GemmOp::kSdd, 256, true>(map_a, map_a, map_b, map_out, params, as_stream(stream),
@@ -73,10 +80,11 @@ int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const in
 extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_t* row_block_expert,
                       const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model,
                       int32_t ffn_dim, int32_t num_experts, int32_t num_row_blocks, int apply_gelu,
-                      int skip_padding_rows, int32_t* dev_status, sb_stream_t stream) {
+                      int skip_padding_rows, const int32_t* padded_offsets, int32_t* dev_status, sb_stream_t stream) {
   sb::clear_error();
   return sb::sdd_launch(x, w1, row_token, row_block_expert, row_offsets, h_blocks, num_tokens, d_model, ffn_dim,
-                        num_experts, num_row_blocks, apply_gelu, skip_padding_rows, nullptr, dev_status, stream);
+                        num_experts, num_row_blocks, apply_gelu, skip_padding_rows, padded_offsets, nullptr, dev_status,
+                        stream);
 }
 
 extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const int32_t* row_slot,
@@ -109,6 +117,6 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
   dp.vecs_per_row = d_model / 8;
   dp.num_pairs = num_ranks * experts_local;
   return sdd_launch(recv_rows, w1, row_slot, row_block_expert, row_offsets, h_blocks,
-                    static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, &dp,
-                    dev_status, stream);
+                    static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, nullptr,
+                    &dp, dev_status, stream);
 }

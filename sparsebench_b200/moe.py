@@ -15,7 +15,7 @@ from collections.abc import Callable
 import torch
 
 from sparsebench_b200 import _C
-from sparsebench_b200.routing import route_device
+from sparsebench_b200.routing import route_and_layout, route_device
 from sparsebench_b200.spmm import combine, dsd, sdd
 
 BLOCK_SIZE = 128
@@ -50,9 +50,33 @@ def moe_forward(
     mark("routing")
     # Padding rows (up to 127 per expert) are neither stored by SDD nor read or stored by DSD in
     # whole groups of 32: nothing reads them, and H is the largest activation stream of the layer.
-    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True, layout_from_routing=True)
     mark("SDD + GELU (fused)")
-    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True)
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True,
+            layout_from_routing=True)
+    mark("DSD")
+    out = combine(y, expert_weight, topo)
+    mark("combine")
+    return out
+
+
+def moe_forward_from_logits(x: torch.Tensor, router_logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+                            k: int = 2, mark: Callable[[str], None] = _no_mark) -> torch.Tensor:
+    """moe_forward with the router in front: router_logits [T, E] -> top-k experts and a softmax over the k
+    picked logits (reference: sparsebench/reference.py:19-29), then the layer. The router is part of the
+    routing kernel (one launch from logits to layout), so the layer stays at four launches and the host
+    never sees an expert id."""
+    num_experts, d_model, ffn_dim = w1.shape
+    if w2.shape != (num_experts, ffn_dim, d_model):
+        raise ValueError(f"w2 must be {(num_experts, ffn_dim, d_model)}, got {tuple(w2.shape)}")
+    if x.shape[1] != d_model or router_logits.shape != (x.shape[0], num_experts):
+        raise ValueError("x must be [T, D] and router_logits [T, E]")
+    _, expert_weight, topo = route_and_layout(router_logits, k, ffn_dim, BLOCK_SIZE)
+    mark("routing")
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True, layout_from_routing=True)
+    mark("SDD + GELU (fused)")
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True,
+            layout_from_routing=True)
     mark("DSD")
     out = combine(y, expert_weight, topo)
     mark("combine")
@@ -84,6 +108,7 @@ def moe_forward_assigned(
     token_of_copy = token_of_copy.contiguous()
     # With k = 1 routing's row_token holds copy indices (-1 for padding): map them to tokens.
     topo = dataclasses.replace(topo, row_token=_C.remap_rows_cuda(topo.row_token, token_of_copy, num_tokens))
-    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True)
-    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True)
+    h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True, layout_from_routing=True)
+    y = dsd(h, w2.view(num_experts * ffn_dim, d_model), topo, version=5, skip_padding_rows=True,
+            layout_from_routing=True)
     return _C.combine_assigned_cuda(y, topo.copy_row, token_of_copy, weight_of_copy, num_tokens)

@@ -72,15 +72,15 @@ def test_route_workspace_is_zero_for_the_single_launch_shape(lib: ctypes.CDLL) -
 
 def test_null_and_shape_errors_are_reported_before_any_launch(lib: ctypes.CDLL) -> None:
     assert lib.sb_arch_probe(None, 0, None) == 1 and b"must be positive" in lib.sb_last_error()
-    assert lib.sb_sdd(None, None, None, None, None, None, 4, 96, 256, 2, 1, 1, 0, None, None) == 1
+    assert lib.sb_sdd(None, None, None, None, None, None, 4, 96, 256, 2, 1, 1, 0, None, None, None) == 1
     one = ctypes.c_void_p(256)  # never dereferenced: the size checks come first
-    assert lib.sb_sdd(one, one, one, one, one, one, 4, 96, 256, 2, 1, 1, 0, None, None) == 1
+    assert lib.sb_sdd(one, one, one, one, one, one, 4, 96, 256, 2, 1, 1, 0, None, None, None) == 1
     assert b"multiple of 64" in lib.sb_last_error()
-    assert lib.sb_sdd(one, one, one, one, one, one, 4, 128, 128, 2, 1, 1, 0, None, None) == 1
+    assert lib.sb_sdd(one, one, one, one, one, one, 4, 128, 128, 2, 1, 1, 0, None, None, None) == 1
     assert b"multiple of 256" in lib.sb_last_error()
-    assert lib.sb_dsd(one, 4, one, 256, 100, one, one, 2, 128, 0, None, one, None, None) == 1
+    assert lib.sb_dsd(one, 4, one, 256, 100, one, one, 2, 128, 0, None, one, None, 0, None, None) == 1
     assert b"multiple of 128" in lib.sb_last_error()
-    assert lib.sb_dsd(one, 4, one, 256, 128, one, one, 2, 32, 0, None, one, None, None) == 1
+    assert lib.sb_dsd(one, 4, one, 256, 128, one, one, 2, 32, 0, None, one, None, 0, None, None) == 1
     assert b"64 or 128" in lib.sb_last_error()
     assert lib.sb_combine(one, one, one, 0, one, 4, 2, 12, None) == 1
     assert b"multiple of 8" in lib.sb_last_error()

@@ -107,3 +107,64 @@ def test_rejects_bad_input() -> None:
         route(torch.zeros(4, 4, device="cuda"), 5)
     with pytest.raises(RuntimeError, match="k <= min"):
         route(torch.zeros(4, 16, device="cuda"), 9)
+
+
+# ---- router fused into the routing kernel: logits -> layout in one launch ----------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize(("num_tokens", "num_experts", "k", "block_size"),
+                         [(1, 4, 2, 16), (13, 8, 1, 4), (513, 8, 2, 128), (4096, 64, 2, 128), (1000, 256, 4, 128),
+                          (300, 33, 8, 16), (16384, 128, 2, 128), (77, 64, 3, 128), (20000, 64, 2, 128), (64, 300, 2, 128)])
+def test_route_and_layout_equals_router_then_routing(num_tokens, num_experts, k, block_size, dtype) -> None:
+    # Covers the one-launch form (k a power of two, E <= 256, T*k <= 32768) and the shapes that fall back to two
+    # launches (k = 3, T*k > 32768, E > 256): identical results either way, and identical to the oracle.
+    import numpy as np
+
+    from oracle import layout as L
+    from sparsebench_b200 import route_and_layout
+
+    if dtype == torch.bfloat16 and num_experts > 128:
+        pytest.skip("bf16 cannot hold that many distinct logits in [-4, 4]")
+    g = torch.Generator().manual_seed(num_tokens * 7 + num_experts)
+    grid = torch.linspace(-4.0, 4.0, num_experts).to(dtype)
+    logits = torch.stack([grid[torch.randperm(num_experts, generator=g)] for _ in range(num_tokens)])
+    ffn_dim = 2 * block_size
+    idx, weight, topo = route_and_layout(logits.cuda(), k, ffn_dim, block_size)
+    want_idx, want_weight = M.route(logits, k)
+    assert idx.dtype == torch.int64 and weight.dtype == dtype
+    assert torch.equal(idx.cpu(), want_idx)
+    tol = {"rtol": 1e-5, "atol": 1e-6} if dtype == torch.float32 else {"rtol": 2**-7, "atol": 1e-3}
+    torch.testing.assert_close(weight.cpu().float(), want_weight.float(), **tol)
+    want = L.device_layout(want_idx, num_experts, ffn_dim, block_size)
+    for field in L.Layout.FIELDS:
+        assert np.array_equal(getattr(topo, field).cpu().numpy(), getattr(want, field)), field
+    assert int(topo.error.item()) == 0
+
+
+def test_layer_from_logits_in_a_graph_with_new_logits() -> None:
+    from sparsebench_b200 import moe_forward_from_logits
+
+    g = torch.Generator().manual_seed(3)
+    num_tokens, num_experts, d_model, ffn_dim = 1024, 16, 256, 512
+    x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
+    w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16().cuda()
+    w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
+    logits = torch.randn(num_tokens, num_experts, generator=g).bfloat16().cuda()
+    stages: list[str] = []
+    moe_forward_from_logits(x, logits, w1, w2, mark=stages.append)
+    assert stages == ["routing", "SDD + GELU (fused)", "DSD", "combine"]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        moe_forward_from_logits(x, logits, w1, w2)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = moe_forward_from_logits(x, logits, w1, w2)
+    new_logits = torch.randn(num_tokens, num_experts, generator=g).bfloat16()
+    logits.copy_(new_logits.cuda())
+    graph.replay()
+    torch.cuda.synchronize()
+    idx, weight = M.route(new_logits, 2)
+    expected = M.moe_reference(x.float().cpu(), idx, weight.float(), w1.float().cpu(), w2.float().cpu())
+    torch.testing.assert_close(out.float().cpu(), expected, rtol=2e-2, atol=2e-2)
