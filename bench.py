@@ -378,10 +378,10 @@ def stage_roofline(cfg: LayerConfig, layer, dev, flush, iters: int, peaks: tuple
         state["topo"] = route_device(dev.expert_idx, cfg.num_experts, cfg.ffn_dim, 128)
 
     def stage_sdd(state: dict) -> None:
-        state["h"] = sdd(dev.x, dev.w1, state["topo"], skip_padding_rows=True)
+        state["h"] = sdd(dev.x, dev.w1, state["topo"], skip_padding_rows=True, layout_from_routing=True)
 
     def stage_dsd(state: dict) -> None:
-        state["y"] = dsd(state["h"], w2_cat, state["topo"], version=5, skip_padding_rows=True)
+        state["y"] = dsd(state["h"], w2_cat, state["topo"], version=5, skip_padding_rows=True, layout_from_routing=True)
 
     def stage_combine(state: dict) -> None:
         state["out"] = combine(state["y"], dev.expert_weight, state["topo"])

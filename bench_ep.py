@@ -376,8 +376,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         torch.cuda.synchronize()
 
     # Kernels of this library per step: sort, plan, (pack | push counts + push rows + barrier),
-    # slot experts, routing (1 launch, 3 beyond 262144 slots), SDD, DSD, (pack | [push rows +] barrier), combine.
-    route_launches = 1 if world * moe.capacity <= 262144 else 3
+    # slot experts, routing (1 launch, 3 beyond 131072 slots), SDD, DSD, (pack | [push rows +] barrier), combine.
+    route_launches = 1 if world * moe.capacity <= 131072 else 3
     fused_return = moe.peer is not None and moe.fuse_return
     fused_dispatch = moe.peer is not None and moe.fuse_dispatch
     if fused_dispatch:

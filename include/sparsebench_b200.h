@@ -109,7 +109,7 @@ int sb_route(const void* expert_idx, int idx_is_i64, int64_t n_copies, int32_t k
  * until the process exits. It calls no cudaMalloc, cudaFree or other allocating routine.
  *   - Sizes whose scratch (sb_route_workspace_bytes) exceeds the array are rejected with
  *     SB_ERR_INVALID_ARGUMENT and a message that names both numbers; 1 MiB covers e.g. 500 000
- *     copies over 1024 experts, or 8 million copies over 64 experts. Up to 262144 copies the
+ *     copies over 1024 experts, or 8 million copies over 64 experts. Up to 131072 copies the
  *     routing is a single launch and no scratch is touched at all.
  *   - The first call on a device looks the array's device address up (once per device, with that
  *     device current). Make that first call outside of any stream capture.
@@ -146,6 +146,12 @@ int sb_sdd(const void* x, const void* w1, const int32_t* row_token, const int32_
            const int32_t* row_offsets, void* h_blocks, int64_t num_tokens, int32_t d_model, int32_t ffn_dim,
            int32_t num_experts, int32_t num_row_blocks, int apply_gelu, int skip_padding_rows,
            const int32_t* padded_offsets, int32_t* dev_status, sb_stream_t stream);
+
+/*
+ * Diagnostic: how many pairs of thread blocks of the cta_group::2 matmul kernel can be resident at once on the
+ * current device (its launches use exactly that many), or -1 after recording an error. Host-side query.
+ */
+int sb_gemm_pair_clusters(void);
 
 /*
  * DSD: y[rb*bs + r][:] = sum over p in [row_offsets[rb], row_offsets[rb+1]) of
@@ -228,6 +234,24 @@ int sb_remap_rows(const int32_t* row_copy, const void* token_of_copy, int token_
 int sb_combine_assigned(const void* y, const int32_t* copy_row, const void* token_of_copy, int token_is_i64,
                         const void* weight, int weight_dtype, float* accumulator, void* out, int64_t num_copies,
                         int64_t num_tokens, int32_t d_model, sb_stream_t stream);
+
+/*
+ * Token rounding on the device: top-k routing whose per-expert token counts are moved to the nearest
+ * multiple of `tile` (ties down, at most the largest multiple that fits in T) by dropping an expert's
+ * lowest-scoring picks or adding the best-scoring tokens that did not pick it; equal scores rank in token
+ * order; a token's weights are its kept scores renormalised to sum to 1. Replaces the reference's
+ * host-synchronising sparsebench/token_rounding.py:58-81 (its nonzero() learns the list length on the
+ * host). Here the list has the fixed length sb_token_rounding_capacity = T*k + E*(tile/2), is written in
+ * the reference's order (token-major, expert ascending), and entries past *num_copies carry expert -1,
+ * token 0, weight 0: sb_route skips them, so the list feeds the assignment-list layer as it is.
+ * scores: fp32 [T, E] (router probabilities), E <= 1024, k <= 8. workspace:
+ * sb_token_rounding_workspace_bytes bytes of device memory.
+ */
+int64_t sb_token_rounding_capacity(int64_t num_tokens, int32_t num_experts, int32_t k, int32_t tile);
+size_t sb_token_rounding_workspace_bytes(int64_t num_tokens, int32_t num_experts, int32_t k);
+int sb_token_rounding(const float* scores, int64_t num_tokens, int32_t num_experts, int32_t k, int32_t tile,
+                      int32_t* token_of_copy, int32_t* expert_of_copy, float* weight_of_copy, int32_t* num_copies,
+                      void* workspace, sb_stream_t stream);
 
 /*
  * ---- Expert-parallel plumbing (no counterpart in the reference, which is single-GPU) ----------

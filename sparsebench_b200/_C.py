@@ -300,6 +300,28 @@ def combine_assigned_cuda(y: torch.Tensor, copy_row: torch.Tensor, token_of_copy
     return out
 
 
+def token_rounding_cuda(scores: torch.Tensor, k: int, tile: int):
+    """(token_of_copy int32 [cap], expert_of_copy int32 [cap], weight_of_copy fp32 [cap], num_copies int32 [1]) with
+    cap = T*k + E*(tile // 2): the reference's token_rounding (sparsebench/token_rounding.py:58-81) without its host
+    sync. Entries past num_copies carry expert -1 (skipped by routing) and weight 0."""
+    lib = _lib.load()
+    _check(scores.is_cuda and scores.dim() == 2 and scores.is_contiguous() and scores.dtype == torch.float32,
+           "scores must be a contiguous [T, E] float32 CUDA tensor")
+    num_tokens, num_experts = scores.shape
+    _check(num_tokens > 0 and 0 < k <= num_experts and tile > 0, f"need [T, E] scores with 0 < k <= E and tile > 0, got k={k}")
+    cap = lib.sb_token_rounding_capacity(num_tokens, num_experts, k, tile)
+    work = lib.sb_token_rounding_workspace_bytes(num_tokens, num_experts, k)
+    with torch.cuda.device(scores.device):
+        token = torch.empty(cap, dtype=torch.int32, device=scores.device)
+        expert = torch.empty(cap, dtype=torch.int32, device=scores.device)
+        weight = torch.empty(cap, dtype=torch.float32, device=scores.device)
+        count = torch.empty(1, dtype=torch.int32, device=scores.device)
+        scratch = torch.empty((work + 3) // 4, dtype=torch.int32, device=scores.device)
+        _lib.check(lib.sb_token_rounding(_ptr(scores), num_tokens, num_experts, k, tile, _ptr(token), _ptr(expert),
+                                         _ptr(weight), _ptr(count), _ptr(scratch), _stream()))
+    return token, expert, weight, count
+
+
 # ---- expert-parallel plumbing (no counterpart in the reference's extension) ----------------------
 
 def sort_copies_cuda(expert_idx: torch.Tensor, num_experts: int) -> list[torch.Tensor]:

@@ -8,10 +8,12 @@ missing. There is no CPU or PyTorch fallback.
 
 from sparsebench_b200.moe import moe_forward, moe_forward_assigned, moe_forward_from_logits
 from sparsebench_b200.routing import DeviceTopology, build_topology_cuda, route, route_and_layout, route_device
+from sparsebench_b200.rounding import DeviceAssignments, moe_forward_rounded, token_rounding
 from sparsebench_b200.spmm import combine, dsd, sdd
 from sparsebench_b200.topology import Topology
 
 __all__ = [
+    "DeviceAssignments",
     "DeviceTopology",
     "Topology",
     "build_topology_cuda",
@@ -20,9 +22,11 @@ __all__ = [
     "moe_forward",
     "moe_forward_assigned",
     "moe_forward_from_logits",
+    "moe_forward_rounded",
     "route",
     "route_and_layout",
     "route_device",
     "sdd",
+    "token_rounding",
 ]
 __version__ = "0.1.0"

@@ -15,7 +15,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC_DIR = PACKAGE_DIR / "csrc"
 LIB_PATH = PACKAGE_DIR / "libsparsebench_b200.so"
-SOURCES = ["common.cu", "routing.cu", "combine.cu", "tensormap.cu", "sdd.cu", "dsd.cu", "assigned.cu", "router.cu", "ep.cu"]
+SOURCES = ["common.cu", "routing.cu", "combine.cu", "tensormap.cu", "sdd.cu", "dsd.cu", "assigned.cu", "router.cu", "ep.cu", "rounding.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

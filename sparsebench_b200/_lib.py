@@ -29,6 +29,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "sb_route_static_scratch": (c_int, [_P, c_int, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
                                         _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_sdd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int32, c_int32, c_int32, c_int32, c_int, c_int, _P, _P, _P]),
+    "sb_gemm_pair_clusters": (c_int, []),
     "sb_dsd": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, c_int32, c_int, _P, _P, _P, c_int32, _P, _P]),
     "sb_combine": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int32, c_int32, _P]),
     "sb_router_topk": (c_int, [_P, c_int, c_int64, c_int32, c_int32, _P, c_int, _P, _P]),
@@ -37,6 +38,9 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                      _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_remap_rows": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, c_int64, _P]),
     "sb_combine_assigned": (c_int, [_P, _P, _P, c_int, _P, c_int, _P, _P, c_int64, c_int64, c_int32, _P]),
+    "sb_token_rounding_capacity": (c_int64, [c_int64, c_int32, c_int32, c_int32]),
+    "sb_token_rounding_workspace_bytes": (c_size_t, [c_int64, c_int32, c_int32]),
+    "sb_token_rounding": (c_int, [_P, c_int64, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P, _P]),
     "sb_ep_plan": (c_int, [_P, _P, _P, c_int64, c_int32, c_int32, c_int32, _P, _P, _P, _P]),
     "sb_ep_slot_experts": (c_int, [_P, c_int32, c_int32, c_int32, _P, _P]),
     "sb_gather_rows": (c_int, [_P, _P, _P, c_int64, c_int32, _P]),

@@ -225,6 +225,9 @@ bsr_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int32_t k_steps = k_steps_of(info);
         const int32_t a_rows = (kIsSdd || !info.valid) ? 0 : (p.skip_padding ? info.groups * 32 : Cfg::kTileM);
         const int32_t b_col = info.n0 + static_cast<int32_t>(rank) * (kTileN / 2);
+        // DSD: the column index of block j + 1 is fetched while block j is issued, off the issue path.
+        int32_t col_block = 0;
+        int32_t col_block_next = (!kIsSdd && info.blocks > 0) ? __ldg(p.col_indices + info.begin0) : 0;
         for (int32_t ks = 0; ks < k_steps; ++ks) {
           if (!ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, abort_word)) {
             give_up(SB_DEV_TIMEOUT_PRODUCER);
@@ -247,7 +250,11 @@ bsr_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 ptx::tma_load_2d_hint_pair(a_base + stage * Cfg::kABytes + g * (32 * 128), &map_a_rows32, k_half,
                                            (info.begin + j) * Cfg::kTileM + g * 32, bar, stream_once);
             }
-            b_row = __ldg(p.col_indices + info.begin0 + j) * Cfg::kTileM + k_half;
+            if ((ks & 1) == 0) {
+              col_block = col_block_next;
+              if (j + 1 < info.blocks) col_block_next = __ldg(p.col_indices + info.begin0 + j + 1);
+            }
+            b_row = col_block * Cfg::kTileM + k_half;
           }
           const uint32_t b_dst = b_base + stage * Cfg::kBBytes;
 #pragma unroll
@@ -482,6 +489,35 @@ inline bool use_pair_kernel(const int32_t* padded_offsets, int32_t num_row_block
   return false;  // PENDING: off unless asked for, until measured on the GPU
 }
 
+// How many pairs of this kernel can be resident at once on `device`. The tile walk is static (tile, tile +
+// clusters, ...), so every launched cluster must be resident together: a pair needs two free SMs of one GPC, and
+// not every SM of the chip can be paired. Asked once per device (a host-side query, no synchronisation).
+template <GemmOp kOp>
+int pair_resident_clusters(int device, int sm_count, int* out) {
+  static std::atomic<int> cached[kMaxDevices] = {};
+  int fit = cached[device].load(std::memory_order_acquire);
+  if (fit == 0) {
+    if (int rc = prepare_pair_kernel<kOp>(device)) return rc;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2));
+    config.blockDim = dim3(PairConfig<kOp>::kThreads);
+    config.dynamicSmemBytes = PairConfig<kOp>::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    const cudaError_t occ = cudaOccupancyMaxActiveClusters(&fit, bsr_gemm_pair_kernel<kOp>, &config);
+    if (occ != cudaSuccess || fit < 1)
+      return fail(SB_ERR_CUDA, "pair kernel: cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(occ));
+    cached[device].store(fit, std::memory_order_release);
+  }
+  *out = fit;
+  return SB_OK;
+}
+
 template <GemmOp kOp>
 int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, const CUtensorMap& map_b,
                      const CUtensorMap& map_out, const GemmParams& params, const int32_t* padded_offsets,
@@ -498,11 +534,8 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, 
   pp.num_experts = num_experts;
   // Worst case number of pair tiles: every expert may end in a half pair.
   const int64_t tiles = static_cast<int64_t>((params.num_row_blocks + num_experts + 1) / 2) * params.num_slices;
-  int64_t clusters = info->sm_count / 2;
-  if (tiles < clusters) clusters = tiles;
-  if (clusters < 1) clusters = 1;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+  config.gridDim = dim3(static_cast<unsigned>(info->sm_count / 2 * 2));
   config.blockDim = dim3(Cfg::kThreads);
   config.dynamicSmemBytes = Cfg::kSmemBytes;
   config.stream = stream;
@@ -513,6 +546,13 @@ int launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, 
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = 1;
+  int fit = 0;
+  if (int rc = pair_resident_clusters<kOp>(device, info->sm_count, &fit)) return rc;
+  int64_t clusters = fit;
+  if (clusters > info->sm_count / 2) clusters = info->sm_count / 2;
+  if (tiles < clusters) clusters = tiles;
+  if (clusters < 1) clusters = 1;
+  config.gridDim = dim3(static_cast<unsigned>(2 * clusters));
   const cudaError_t err = cudaLaunchKernelEx(&config, bsr_gemm_pair_kernel<kOp>, map_a, map_a_rows32, map_b, map_out, pp);
   if (err != cudaSuccess) return fail(SB_ERR_CUDA, "%s (pair kernel): %s", what, cudaGetErrorString(err));
   return check_launch(what);

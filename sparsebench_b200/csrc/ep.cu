@@ -113,9 +113,7 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ in
        j += warps) {
     const int32_t row = __ldg(index + j);
     if (row < 0) continue;
-    const uint4* s = src + static_cast<int64_t>(row) * vecs_per_row;
-    uint4* d = out + j * vecs_per_row;
-    for (int32_t v = lane; v < vecs_per_row; v += 32) d[v] = __ldg(s + v);
+    copy_row_warp(src + static_cast<int64_t>(row) * vecs_per_row, out + j * vecs_per_row, vecs_per_row, lane);
   }
 }
 
@@ -133,9 +131,8 @@ push_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ inde
     if (row < 0) continue;
     const int32_t peer = static_cast<int32_t>(j / capacity);
     const int64_t i = j - static_cast<int64_t>(peer) * capacity;
-    const uint4* s = src + static_cast<int64_t>(row) * vecs_per_row;
-    uint4* d = peer_base[peer] + (static_cast<int64_t>(my_rank) * capacity + i) * vecs_per_row;
-    for (int32_t v = lane; v < vecs_per_row; v += 32) d[v] = __ldg(s + v);
+    copy_row_warp(src + static_cast<int64_t>(row) * vecs_per_row,
+                  peer_base[peer] + (static_cast<int64_t>(my_rank) * capacity + i) * vecs_per_row, vecs_per_row, lane);
   }
 }
 

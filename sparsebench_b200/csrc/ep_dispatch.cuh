@@ -63,6 +63,22 @@ __device__ __forceinline__ uint64_t dispatch_timer_ns() {
   return t;
 }
 
+// One warp copies one row of `vecs` 16-byte vectors. Up to eight loads per lane are issued before the first
+// store: written as "d[v] = s[v]" in a loop, every load would wait for the store before it (the two pointers
+// may alias as far as the compiler knows), one memory latency per 512 bytes.
+__device__ __forceinline__ void copy_row_warp(const uint4* __restrict__ src, uint4* __restrict__ dst, int32_t vecs,
+                                              int lane) {
+  for (int32_t v0 = lane; v0 < vecs; v0 += 32 * 8) {
+    uint4 held[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (v0 + 32 * q < vecs) held[q] = __ldg(src + v0 + 32 * q);
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (v0 + 32 * q < vecs) dst[v0 + 32 * q] = held[q];
+  }
+}
+
 // One warp's share of the source side: chunks worker, worker + num_workers, ... of the push plan.
 __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker, int num_workers, int lane) {
   const int32_t pairs = dp.num_pairs;
@@ -90,9 +106,7 @@ __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker
                    (static_cast<int64_t>(dp.my_rank) * dp.capacity + __ldg(slot_start + q) + j0) * dp.vecs_per_row;
       for (int32_t r = 0; r < rows; ++r) {
         const uint4* src = dp.x + static_cast<int64_t>(__ldg(dp.sorted_token + pos0 + r)) * dp.vecs_per_row;
-        uint4* out = dst + static_cast<int64_t>(r) * dp.vecs_per_row;
-#pragma unroll 8
-        for (int32_t v = lane; v < dp.vecs_per_row; v += 32) out[v] = __ldg(src + v);
+        copy_row_warp(src, dst + static_cast<int64_t>(r) * dp.vecs_per_row, dp.vecs_per_row, lane);
       }
       __threadfence_system();  // this lane's rows are in the destination's memory before the count below
     }

@@ -15,7 +15,7 @@
 // two launches always agree.
 //
 // Two launch shapes:
-//   cluster (n <= 262144 copies): ONE launch of a thread-block cluster (1-8 blocks of 1024 threads)
+//   cluster (n <= 131072 copies): ONE launch of a thread-block cluster (1-8 blocks of 1024 threads)
 //       does count, scan, scatter and the layout arrays; the blocks share their per-expert counts
 //       through distributed shared memory. This is the hot-path shape (8192 copies per layer call).
 //   large: chunk histograms -> one-block scan -> scatter + layout, three launches and a scratch
@@ -39,8 +39,8 @@ constexpr int kMaxExperts = 1024;  // one thread per expert in the scan block (r
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kClusterThreads = 1024;
 constexpr int kMaxClusterBlocks = 8;    // the portable cluster size limit
-constexpr int kMaxRunSteps = 32;        // 32-copy steps a warp keeps in registers
-constexpr int64_t kClusterMaxCopies = static_cast<int64_t>(kMaxClusterBlocks) * kClusterThreads * kMaxRunSteps;  // 262144
+constexpr int kMaxRunSteps = 16;        // 32-copy steps a warp keeps in registers (more would spill at 1024 threads)
+constexpr int64_t kClusterMaxCopies = static_cast<int64_t>(kMaxClusterBlocks) * kClusterThreads * kMaxRunSteps;  // 131072
 constexpr int kChunkThreads = 256;
 constexpr int kChunkWarps = kChunkThreads / 32;
 constexpr int kChunkCopies = 2048;  // copies per block in the large shape
@@ -180,18 +180,26 @@ struct LogitSource {
 };
 
 // One warp walks its run 32 copies per step, in copy order, and adds it to its private counters.
-// For every copy it also returns pos = the number of copies of the same expert that come earlier in
+// For every copy it also finds pos = the number of copies of the same expert that come earlier in
 // this run: the lanes holding the same expert below this one count towards pos, and the lowest of
 // them alone reads and advances the counter (one writer per expert per step) and hands the old
 // value to its peers. Nothing here depends on timing, so the order is stable.
+// The result replaces the id in place: ids[it] becomes pos << 16 | (id & 0xffff) (an id is < 1024 or -1,
+// a pos is < the run length <= 1024), so that a long run costs one register per copy, not two.
+__device__ __forceinline__ int32_t packed_id(int32_t packed) {
+  const int32_t low = packed & 0xffff;
+  return low == 0xffff ? -1 : low;
+}
+__device__ __forceinline__ int32_t packed_pos(int32_t packed) { return static_cast<int32_t>(static_cast<uint32_t>(packed) >> 16); }
+
 template <int kIters>
-__device__ __forceinline__ void rank_run(const int32_t (&ids)[kIters], int64_t begin, int64_t end, int id_bits,
-                                         int32_t* counters, int lane, int32_t (&pos)[kIters]) {
+__device__ __forceinline__ void rank_run(int32_t (&ids)[kIters], int64_t begin, int64_t end, int id_bits,
+                                         int32_t* counters, int lane) {
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
-    pos[it] = 0;
-    if (begin + it * 32 >= end) continue;  // uniform across the warp
     const int32_t e = ids[it];
+    ids[it] = e & 0xffff;
+    if (begin + it * 32 >= end) continue;  // uniform across the warp
     const unsigned peers = same_expert_lanes(e, e >= 0, id_bits);
     int32_t before = 0;
     if (peers != 0 && (peers & ((1u << lane) - 1u)) == 0) {
@@ -200,24 +208,23 @@ __device__ __forceinline__ void rank_run(const int32_t (&ids)[kIters], int64_t b
     }
     const int leader = peers != 0 ? __ffs(peers) - 1 : lane;
     before = __shfl_sync(kFullMask, before, leader);
-    pos[it] = before + __popc(peers & ((1u << lane) - 1u));
+    ids[it] |= (before + __popc(peers & ((1u << lane) - 1u))) << 16;
     __syncwarp();
   }
 }
 
 // Places a run. bases[e] = copies of expert e before this run (earlier chunks and warps).
 template <int kIters>
-__device__ __forceinline__ void scatter_run(const int32_t (&ids)[kIters], const int32_t (&pos)[kIters], int64_t begin,
-                                            int64_t end, int32_t k, const int32_t* bases,
-                                            const int32_t* padded_offsets, int32_t* __restrict__ copy_row,
-                                            int32_t* __restrict__ row_token, int lane) {
+__device__ __forceinline__ void scatter_run(const int32_t (&ranked)[kIters], int64_t begin, int64_t end, int32_t k,
+                                            const int32_t* bases, const int32_t* padded_offsets,
+                                            int32_t* __restrict__ copy_row, int32_t* __restrict__ row_token, int lane) {
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
     const int64_t c = begin + it * 32 + lane;
     if (c >= end) continue;
-    const int32_t e = ids[it];
+    const int32_t e = packed_id(ranked[it]);
     if (e >= 0) {
-      const int32_t row = padded_offsets[e] + bases[e] + pos[it];
+      const int32_t row = padded_offsets[e] + bases[e] + packed_pos(ranked[it]);
       copy_row[c] = row;
       row_token[row] = static_cast<int32_t>(static_cast<uint32_t>(c) / static_cast<uint32_t>(k));
     } else {
@@ -343,8 +350,7 @@ route_cluster_kernel(const Source source, int32_t n, int32_t k, int32_t num_expe
   const bool bad = source.template load<kIters>(begin, end, lane, ids);
   for (int i = threadIdx.x; i < kWarps * stride; i += kClusterThreads) counters[i] = 0;
   __syncthreads();
-  int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, id_bits, counters + warp * stride, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, counters + warp * stride, lane);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) *cta_bad = any_bad;
 
@@ -398,7 +404,7 @@ route_cluster_kernel(const Source source, int32_t n, int32_t k, int32_t num_expe
   int32_t* bases = counters + warp * stride;
   for (int i = lane; i < num_experts; i += 32) bases[i] += cta_base[i];
   __syncwarp();
-  scatter_run<kIters>(ids, pos, begin, end, k, bases, offsets, copy_row, layout.row_token, lane);
+  scatter_run<kIters>(ids, begin, end, k, bases, offsets, copy_row, layout.row_token, lane);
   fill_layout(offsets, counts, num_experts, block_size, ffn_blocks, max_row_blocks, layout, cta * kWarps + warp,
               num_ctas * kWarps, lane);
   cluster.sync();  // no block may exit while another still reads its shared memory
@@ -422,8 +428,7 @@ route_chunk_count_kernel(const index_t* __restrict__ expert_idx, int64_t n, int3
   const int64_t end = min(n, begin + kRun);
   int32_t ids[kIters];
   const bool bad = load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
-  int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (threadIdx.x == 0) chunk_error[blockIdx.x] = any_bad;
 
@@ -496,8 +501,7 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
   load_run<index_t, kIters>(expert_idx, begin, end, num_experts, lane, ids);
   for (int i = threadIdx.x; i < kChunkWarps * num_experts; i += kChunkThreads) smem[i] = 0;
   __syncthreads();
-  int32_t pos[kIters];
-  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane, pos);
+  rank_run<kIters>(ids, begin, end, id_bits, smem + warp * num_experts, lane);
   __syncthreads();
   const int32_t* base = chunk_base + static_cast<int64_t>(blockIdx.x) * num_experts;
   for (int e = threadIdx.x; e < num_experts; e += kChunkThreads) {
@@ -511,7 +515,7 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
     }
   }
   __syncthreads();
-  scatter_run<kIters>(ids, pos, begin, end, k, smem + warp * num_experts, padded_offsets, copy_row, layout.row_token,
+  scatter_run<kIters>(ids, begin, end, k, smem + warp * num_experts, padded_offsets, copy_row, layout.row_token,
                       lane);
 }
 
@@ -678,7 +682,6 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
                                                      tokens_per_expert, padded_offsets, copy_row, layout, error)
     if (steps <= 1) SB_ROUTE_CLUSTER(1);
     if (steps <= 4) SB_ROUTE_CLUSTER(4);
-    if (steps <= 16) SB_ROUTE_CLUSTER(16);
     SB_ROUTE_CLUSTER(kMaxRunSteps);
 #undef SB_ROUTE_CLUSTER
   }

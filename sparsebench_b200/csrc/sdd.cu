@@ -120,3 +120,14 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
                     static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, nullptr,
                     &dp, dev_status, stream);
 }
+
+extern "C" int sb_gemm_pair_clusters(void) {
+  using namespace sb;
+  clear_error();
+  int device = 0;
+  const DeviceInfo* info = current_device_info(&device);
+  if (info == nullptr) return -1;
+  int fit = 0;
+  if (pair_resident_clusters<GemmOp::kSdd>(device, info->sm_count, &fit) != SB_OK) return -1;
+  return fit;
+}

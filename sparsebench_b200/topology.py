@@ -15,18 +15,21 @@ import torch
 
 @dataclass(frozen=True)
 class Topology:
-    block_size: int
+    block_size: int  # rows (and columns) of one block of H
     num_experts: int
-    ffn_blocks: int  # F // block_size: column blocks per expert
+    ffn_blocks: int  # how many blocks one expert's F columns make: F // block_size
 
-    tokens_per_expert: torch.Tensor  # [E] int32, real copies per expert
-    padded_offsets: torch.Tensor  # [E+1] int32, first padded row of each expert
-    row_token: torch.Tensor  # [P] int32, source token of each row, -1 = padding
-    copy_row: torch.Tensor  # [T*k] int32, padded row of copy (t, j) at t*k + j
+    # Where the copies went. All int32.
+    tokens_per_expert: torch.Tensor  # [E] copies routed to each expert, before padding
+    padded_offsets: torch.Tensor  # [E+1] row at which each expert's group starts; the last entry is P
+    row_token: torch.Tensor  # [P] which token a row holds; -1 marks a row that only pads its group
+    copy_row: torch.Tensor  # [T*k] the row that copy j of token t (index t*k + j) landed in
 
-    row_block_expert: torch.Tensor  # [P / block_size] int32
-    row_offsets: torch.Tensor  # [P / block_size + 1] int32
-    col_indices: torch.Tensor  # [nnz_blocks] int32
+    # H as a block-sparse matrix: row block rb owns blocks row_offsets[rb] .. row_offsets[rb+1], the block at
+    # position p sits in block column col_indices[p] (its expert's columns).
+    row_block_expert: torch.Tensor  # [P / block_size] the expert a row block belongs to
+    row_offsets: torch.Tensor  # [P / block_size + 1]
+    col_indices: torch.Tensor  # [nnz_blocks]
 
     @property
     def num_rows(self) -> int:

@@ -16,6 +16,9 @@ Writes
   layer_cpu_small.npz  the benchmark's CPU-sized configuration (seed 0, T=512 D=256 F=1024 E=8,
                        fp32): routing, gates, digests of the inputs, every 16th output row of
                        reference.moe_reference and float64 checksums of the whole output.
+  rounding.npz         token_rounding.token_rounding on small score matrices (random softmax scores, and
+                       rows that are permutations of a few values so that columns are full of ties):
+                       scores, and the flat (token, expert, weight) list it returns.
 """
 
 from __future__ import annotations
@@ -34,6 +37,7 @@ if not REFERENCE or not os.path.isdir(os.path.join(REFERENCE, "sparsebench")):
 sys.path.insert(0, REFERENCE)
 
 from sparsebench import reference as ref  # noqa: E402
+from sparsebench import token_rounding as ref_rounding  # noqa: E402
 from sparsebench import topology as ref_topology  # noqa: E402
 from sparsebench import workloads as ref_workloads  # noqa: E402
 
@@ -135,7 +139,33 @@ def layer_cpu_small() -> None:
     )
 
 
+def rounding() -> None:
+    out: dict[str, np.ndarray] = {}
+    names = []
+    cases = [("softmax", 512, 8, 2, 128, 0), ("softmax", 300, 16, 2, 32, 1), ("softmax", 1000, 64, 4, 16, 2),
+             ("softmax", 77, 4, 1, 8, 4), ("softmax", 130, 8, 2, 128, 5), ("ties", 600, 8, 2, 32, 6),
+             ("ties", 257, 16, 4, 16, 7)]
+    for kind, num_tokens, num_experts, k, tile, seed in cases:
+        g = torch.Generator().manual_seed(seed)
+        if kind == "softmax":
+            scores = torch.softmax(torch.randn(num_tokens, num_experts, generator=g), dim=-1)
+        else:  # every row a permutation of the same E distinct values: no ties inside a row, many down a column
+            values = torch.arange(1, num_experts + 1, dtype=torch.float32) / (num_experts * (num_experts + 1) / 2)
+            scores = torch.stack([values[torch.randperm(num_experts, generator=g)] for _ in range(num_tokens)])
+        result = ref_rounding.token_rounding(scores.clone(), k, tile)
+        tag = f"{kind}-T{num_tokens}-E{num_experts}-k{k}-tile{tile}"
+        names.append(tag)
+        out[f"{tag}/meta"] = np.array([k, tile], dtype=np.int64)
+        out[f"{tag}/scores"] = scores.numpy()
+        out[f"{tag}/token"] = result.token.numpy()
+        out[f"{tag}/expert"] = result.expert.numpy()
+        out[f"{tag}/weight"] = result.weight.numpy()
+    out["names"] = np.array(names)
+    np.savez_compressed(HERE / "rounding.npz", **out)
+
+
 if __name__ == "__main__":
+    rounding()
     topology_cases()
     layer_small()
     layer_cpu_small()

@@ -66,7 +66,8 @@ def test_route_sizes_rejects_like_the_reference(lib: ctypes.CDLL, args, text: st
 
 def test_route_workspace_is_zero_for_the_single_launch_shape(lib: ctypes.CDLL) -> None:
     assert lib.sb_route_workspace_bytes(8192, 64) == 0
-    assert lib.sb_route_workspace_bytes(262_144, 1024) == 0
+    assert lib.sb_route_workspace_bytes(131_072, 1024) == 0
+    assert lib.sb_route_workspace_bytes(131_073, 1024) == ((131_073 + 2047) // 2048) * 1025 * 4
     assert lib.sb_route_workspace_bytes(300_000, 1024) == ((300_000 + 2047) // 2048) * 1025 * 4
 
 

@@ -27,7 +27,7 @@ def _inputs(case: str, num_tokens: int, num_experts: int, d_model: int, ffn_dim:
     return x, idx, gate, w1, w2
 
 
-CASES = [("random", 1000, 2, 256, 512), ("skewed", 700, 4, 320, 256), ("empty_middle", 900, 4, 256, 512),
+CASES = [("random", 1000, 2, 256, 512), ("skewed", 700, 4, 512, 256), ("empty_middle", 900, 4, 256, 512),
          ("two_experts_only", 130, 8, 256, 256), ("random", 2100, 3, 512, 1024)]
 
 

@@ -149,7 +149,7 @@ def test_layer_from_logits_in_a_graph_with_new_logits() -> None:
     x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
     w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16().cuda()
     w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
-    logits = torch.randn(num_tokens, num_experts, generator=g).bfloat16().cuda()
+    logits = torch.randn(num_tokens, num_experts, generator=g).cuda()  # fp32: no two logits of a token are equal
     stages: list[str] = []
     moe_forward_from_logits(x, logits, w1, w2, mark=stages.append)
     assert stages == ["routing", "SDD + GELU (fused)", "DSD", "combine"]
@@ -161,7 +161,7 @@ def test_layer_from_logits_in_a_graph_with_new_logits() -> None:
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         out = moe_forward_from_logits(x, logits, w1, w2)
-    new_logits = torch.randn(num_tokens, num_experts, generator=g).bfloat16()
+    new_logits = torch.randn(num_tokens, num_experts, generator=g)
     logits.copy_(new_logits.cuda())
     graph.replay()
     torch.cuda.synchronize()

@@ -56,9 +56,9 @@ def test_matches_oracle_big(case: str, num_experts: int) -> None:
     check_against_oracle(routing_case(case, 160_000, num_experts), num_experts, 128)
 
 
-@pytest.mark.parametrize("num_tokens", [511, 512, 513, 4097, 16385, 40000, 131071, 131072, 131073, 150_000])
+@pytest.mark.parametrize("num_tokens", [511, 512, 513, 4097, 16385, 40000, 65535, 65536, 65537, 131072, 150_000])
 def test_both_launch_shapes_around_their_switches(num_tokens: int) -> None:
-    # Cluster of 1..8 blocks, 1/4/16/32 steps per warp; 262144 copies is the last size the
+    # Cluster of 1..8 blocks, 1/4/16 steps per warp; 131072 copies (65536 tokens here) is the last size the
     # single-launch cluster shape takes, beyond it the three-launch shape with scratch runs.
     idx = routing_case("random", num_tokens, 128)
     check_device_buffers(idx, 128, 512, 128)
