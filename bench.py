@@ -581,12 +581,25 @@ def run_single_gpu(args: argparse.Namespace) -> None:
 
 
 def run_profile(args: argparse.Namespace) -> None:
-    """Three eager layer calls and nothing else: the command to put under ncu."""
-    from sparsebench_b200 import moe_forward
+    """Three eager layer calls and nothing else: the command to put under ncu. With --profile-front-ends the
+    three calls go through the router, the token-rounding and the assignment-list front ends instead, so that
+    their small kernels show up too."""
+    from sparsebench_b200 import moe_forward, moe_forward_from_logits, moe_forward_rounded, route
 
     cfg = CONFIGS[args.workload or "fine_grained"]
     torch.cuda.set_device(0)
     dev = make_layer(cfg, seed=0).to("cuda:0")
+    if args.profile_front_ends:
+        g = torch.Generator().manual_seed(0)
+        logits = torch.randn(cfg.num_tokens, cfg.num_experts, generator=g).to("cuda:0")
+        scores = torch.softmax(logits, dim=-1)
+        for _ in range(3):
+            moe_forward_from_logits(dev.x, logits, dev.w1, dev.w2, k=cfg.k)   # router fused into routing
+            route(logits, cfg.k)                                             # the router as a kernel of its own
+            moe_forward_rounded(dev.x, scores, dev.w1, dev.w2, k=cfg.k)      # rounding, assignment list, scatter-add combine
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": cfg.name, "front_end_rounds": 3}))
+        return
     for _ in range(3):
         moe_forward(dev.x, dev.expert_idx, dev.expert_weight, dev.w1, dev.w2)
     torch.cuda.synchronize()
@@ -629,9 +642,18 @@ def main() -> None:
                         help="N > 1, peer exchange: cut each step into this many pipelined micro-batches "
                              "(0 = the default for this N)")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
+    parser.add_argument("--profile-front-ends", action="store_true",
+                        help="with --profile: run the router, token-rounding and assignment-list front ends of the layer")
+    parser.add_argument("--profile-ep-owner", action="store_true",
+                        help="ONE GPU: rank 0's owner-side kernels of the 8-rank expert-parallel step at full size, "
+                             "exchange buffers in local memory, three times, then exit (for ncu)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.profile:
+    if args.profile_ep_owner:
+        import bench_ep
+
+        bench_ep.run_owner_profile(args)
+    elif args.profile:
         run_profile(args)
     elif args.impl == "reference":
         run_reference_arm(args)

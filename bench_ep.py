@@ -270,6 +270,85 @@ def check_status(moe, device: torch.device, world: int, when: str) -> None:
         raise SystemExit(f"{when}: " + "; ".join(problems))
 
 
+class LocalExchange:
+    """The exchange buffers of `ranks` virtual ranks, all in ONE GPU's memory, with the peer tables pointing at
+    them: lets a single GPU run one rank's kernels of the multi-GPU step at full size (profilers never wrap a
+    multi-rank command). of(r) has the attribute names of sparsebench_b200.ep.PeerExchange."""
+
+    def __init__(self, ranks: int, capacity: int, d_model: int, experts_local: int, device: torch.device) -> None:
+        self.recv = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=device)
+        self.ret = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=device)
+        self.counts = torch.zeros(ranks, ranks, experts_local, dtype=torch.int32, device=device)
+        self.pad = torch.zeros(ranks, ranks, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(ranks, ranks * experts_local, dtype=torch.int32, device=device)
+        self.epoch = [torch.zeros(1, dtype=torch.int32, device=device) for _ in range(ranks)]
+        self.done = [torch.zeros(ranks * experts_local, dtype=torch.int32, device=device) for _ in range(ranks)]
+
+        def table(t: torch.Tensor) -> torch.Tensor:
+            return torch.tensor([t[r].data_ptr() for r in range(ranks)], dtype=torch.int64, device=device)
+
+        self.peer_recv, self.peer_ret = table(self.recv), table(self.ret)
+        self.peer_counts, self.peer_pads, self.peer_flags = table(self.counts), table(self.pad), table(self.flags)
+
+    def of(self, rank: int):
+        import types
+
+        return types.SimpleNamespace(
+            recv=self.recv[rank], ret=self.ret[rank], counts=self.counts[rank], pad=self.pad[rank], flags=self.flags[rank],
+            epoch=self.epoch[rank], done=self.done[rank], peer_recv=self.peer_recv, peer_ret=self.peer_ret,
+            peer_counts=self.peer_counts, peer_pads=self.peer_pads, peer_flags=self.peer_flags)
+
+
+def run_owner_profile(args) -> None:
+    """ONE GPU, the owner-side kernels of rank 0 of the 8-rank expert-parallel step at full size, three times:
+    the other seven ranks' rows are pushed by the stand-alone push kernel first (one virtual rank at a time,
+    nothing waits for a concurrent launch), then rank 0's owner layout, SDD with its own pushes inside, and DSD
+    with the return stores inside. The command to put under a profiler for those kernels."""
+    from sparsebench_b200 import _C
+    from sparsebench_b200.routing import DeviceTopology
+
+    ranks = 8
+    cfg = CONFIGS[args.workload or "expert_parallel"]
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    experts_local = cfg.num_experts // ranks
+    n_copies = cfg.num_tokens * cfg.k
+    capacity = int(math.ceil(3.0 * n_copies / ranks / 128.0)) * 128  # keeps the buffers near 1 GB in total
+    ex = LocalExchange(ranks, capacity, cfg.d_model, experts_local, device)
+    mine = make_layer(cfg, seed=0, token_seed=0, experts=range(experts_local)).to(device)
+    sorts, plans, xs = [], [], []
+    for rank in range(ranks):
+        tokens = make_layer(cfg, seed=0, token_seed=rank, experts=range(0)).to(device)
+        _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(tokens.expert_idx, cfg.num_experts)
+        ex.epoch[rank].fill_(1)
+        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts))
+        sorts.append(sorted_token)
+        xs.append(tokens.x)
+    w2_cat = mine.w2.view(experts_local * cfg.ffn_dim, cfg.d_model)
+    view = ex.of(0)
+    for step in range(3):
+        for rank in range(ranks):
+            ex.epoch[rank].fill_(step + 1)
+        for rank in range(1, ranks):
+            r = ex.of(rank)
+            _C.ep_push_rows_flagged(xs[rank], sorts[rank], plans[rank], ex.peer_recv, ex.peer_flags, r.done, r.epoch, rank,
+                                    experts_local, capacity)
+        torch.cuda.synchronize()
+        topo = DeviceTopology(128, experts_local, cfg.ffn_dim // 128, *_C.ep_owner_layout(view.counts, capacity, cfg.ffn_dim))
+        h = _C.ep_sdd_dispatch(view.recv, mine.w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
+                               topo.col_indices.numel(), xs[0], sorts[0], plans[0], ex.peer_recv, ex.peer_flags, view.flags,
+                               view.done, view.epoch, 0, capacity)
+        _C.ep_dsd_push(h, w2_cat, topo.row_offsets, topo.col_indices, topo.row_token, ex.peer_ret, 0, capacity)
+        torch.cuda.synchronize()
+    status = int(_C.device_status(device).item())
+    rows = int(topo.padded_offsets[-1].item())
+    print(json.dumps({"profile": "expert-parallel owner, rank 0 of 8 on one GPU", "steps": 3, "padded_rows": rows,
+                      "received_rows": int(view.counts.sum().item()), "capacity_rows_per_pair": capacity,
+                      "device_status": status}))
+    if status != 0:
+        raise SystemExit("a bounded device-side wait expired")
+
+
 def workload_config(cfg, world: int) -> dict:
     """The `config` object of the JSON line: the workload only, identical for this arm and the reference arm."""
     return {"workload": cfg.name, "tokens_per_gpu": cfg.num_tokens, "d_model": cfg.d_model, "ffn_dim": cfg.ffn_dim,
