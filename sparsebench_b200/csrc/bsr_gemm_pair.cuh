@@ -226,6 +226,7 @@ bsr_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // ---------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
       const uint64_t stream_once = ptx::policy_evict_first();
+      const uint64_t weight_policy = p.reuse_weights ? ptx::policy_evict_normal() : stream_once;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       TileInfo upcoming = load_tile_info(cluster_id);
@@ -272,7 +273,7 @@ bsr_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t b_dst = b_base + stage * Cfg::kBBytes;
 #pragma unroll
           for (int j = 0; j < Cfg::kBSlabs; ++j)
-            ptx::tma_load_2d_hint_pair(b_dst + j * Cfg::kBSlabBytes, &map_b, b_col + j * 64, b_row, bar, stream_once);
+            ptx::tma_load_2d_hint_pair(b_dst + j * Cfg::kBSlabBytes, &map_b, b_col + j * 64, b_row, bar, weight_policy);
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
       }

@@ -71,6 +71,13 @@ int dsd_launch(const void* h_blocks, int64_t num_blocks, const void* w, int64_t 
   params.my_rank = peer.my_rank;
   params.capacity = peer.capacity;
   params.raster_rows = 1;  // row-block-major: D/256 slices per row block keep an expert's row blocks in one wave
+  // Experts in the matrix, from its shape: w rows / (blocks per row block * block size). Several row blocks per
+  // expert (worst case) means a weight tile has several readers close in time.
+  if (num_blocks > 0 && num_blocks % num_row_blocks == 0) {
+    const int64_t rows_per_expert = num_blocks / num_row_blocks * block_size;
+    if (rows_per_expert > 0 && w_rows % rows_per_expert == 0)
+      params.reuse_weights = weights_reused_in_l2(num_row_blocks, static_cast<int32_t>(w_rows / rows_per_expert)) ? 1 : 0;
+  }
   params.row_token = row_token;
   params.skip_padding = row_token != nullptr ? 1 : 0;
   params.d_model = d_model;

@@ -14,8 +14,10 @@
 //   rounding_select_kernel   one block per expert: target count, then the rank threshold among the
 //                            candidates (its picks when shrinking, the other tokens when growing) by a
 //                            4-pass radix select on the scores, ties resolved in token order; writes keep[t][e]
-//   rounding_emit_kernel     one block: scan of kept-per-token, then (token, expert, weight) in token-major,
-//                            expert-ascending order (the order of the reference's nonzero)
+//   rounding_count_kernel    one warp per token: kept experts per token and the sum of their scores
+//   rounding_scan_kernel     one block: exclusive scan of those counts = every token's place in the list
+//   rounding_emit_kernel     one warp per token: (token, expert, weight) in token-major, expert-ascending order
+//                            (the order of the reference's nonzero); the unused tail gets expert -1
 
 #include "sb_common.cuh"
 
@@ -174,18 +176,42 @@ rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restri
   }
 }
 
+// One warp per token: how many experts kept it and the sum of their scores (fp32, ascending expert order, the
+// order in which the reference's index_add_ sums them on the CPU).
+__global__ void __launch_bounds__(kTopkThreads)
+rounding_count_kernel(const float* __restrict__ scores, const uint8_t* __restrict__ keep, int64_t num_tokens,
+                      int32_t num_experts, int32_t* __restrict__ kept_per_token, float* __restrict__ kept_sum) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); t < num_tokens; t += warps) {
+    int32_t count = 0;
+    float sum = 0.0f;
+    for (int32_t e0 = 0; e0 < num_experts; e0 += 32) {
+      const int32_t e = e0 + lane;
+      const bool kept = e < num_experts && keep[t * num_experts + e] != 0;
+      const float v = kept ? __ldg(scores + t * num_experts + e) : 0.0f;
+      const unsigned mask = __ballot_sync(0xffffffffu, kept);
+      count += __popc(mask);
+      // Add this step's kept scores in lane (= expert) order, one after the other, to keep the summation order.
+      for (unsigned rest = mask; rest != 0; rest &= rest - 1) sum += __shfl_sync(0xffffffffu, v, __ffs(rest) - 1);
+    }
+    if (lane == 0) {
+      kept_per_token[t] = count;
+      kept_sum[t] = sum;
+    }
+  }
+}
+
+// One block: kept_per_token becomes its exclusive scan, *num_copies the total (cut at the capacity).
 __global__ void __launch_bounds__(kEmitThreads, 1)
-rounding_emit_kernel(const float* __restrict__ scores, const uint8_t* __restrict__ keep, int64_t num_tokens,
-                     int32_t num_experts, int64_t capacity, int32_t* __restrict__ token_of_copy,
-                     int32_t* __restrict__ expert_of_copy, float* __restrict__ weight_of_copy,
+rounding_scan_kernel(int32_t* __restrict__ kept_per_token, int64_t num_tokens, int64_t capacity,
                      int32_t* __restrict__ num_copies) {
-  __shared__ int32_t scratch[33];
+  __shared__ int32_t scratch[32];
   const int64_t per_thread = (num_tokens + kEmitThreads - 1) / kEmitThreads;
   const int64_t t_begin = min(num_tokens, static_cast<int64_t>(threadIdx.x) * per_thread);
   const int64_t t_end = min(num_tokens, t_begin + per_thread);
   int32_t mine = 0;
-  for (int64_t t = t_begin; t < t_end; ++t)
-    for (int32_t e = 0; e < num_experts; ++e) mine += keep[t * num_experts + e];
+  for (int64_t t = t_begin; t < t_end; ++t) mine += kept_per_token[t];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int32_t inclusive = mine;
   for (int d = 1; d < 32; d <<= 1) {
@@ -195,37 +221,59 @@ rounding_emit_kernel(const float* __restrict__ scores, const uint8_t* __restrict
   if (lane == 31) scratch[warp] = inclusive;
   __syncthreads();
   if (warp == 0) {
-    int32_t s = scratch[lane];
+    int32_t v = scratch[lane];
     for (int d = 1; d < 32; d <<= 1) {
-      const int32_t below = __shfl_up_sync(0xffffffffu, s, d);
-      if (lane >= d) s += below;
+      const int32_t below = __shfl_up_sync(0xffffffffu, v, d);
+      if (lane >= d) v += below;
     }
-    scratch[lane] = s;
+    scratch[lane] = v;
   }
   __syncthreads();
-  int64_t out = (warp > 0 ? scratch[warp - 1] : 0) + inclusive - mine;
-  const int64_t total = scratch[31];
+  int32_t running = (warp > 0 ? scratch[warp - 1] : 0) + inclusive - mine;
   for (int64_t t = t_begin; t < t_end; ++t) {
-    float sum = 0.0f;
-    for (int32_t e = 0; e < num_experts; ++e)
-      if (keep[t * num_experts + e]) sum += scores[t * num_experts + e];
-    for (int32_t e = 0; e < num_experts; ++e) {
-      if (!keep[t * num_experts + e]) continue;
-      if (out < capacity) {
-        token_of_copy[out] = static_cast<int32_t>(t);
-        expert_of_copy[out] = e;
-        weight_of_copy[out] = scores[t * num_experts + e] / sum;
+    const int32_t n = kept_per_token[t];
+    kept_per_token[t] = running;
+    running += n;
+  }
+  if (threadIdx.x == 0) {
+    const int64_t total = scratch[31];
+    *num_copies = static_cast<int32_t>(total < capacity ? total : capacity);
+  }
+}
+
+// One warp per token writes its entries (expert ascending) at its offset; the warps past the last token fill
+// the unused tail of the worst-case sized list with expert -1.
+__global__ void __launch_bounds__(kTopkThreads)
+rounding_emit_kernel(const float* __restrict__ scores, const uint8_t* __restrict__ keep,
+                     const int32_t* __restrict__ offsets, const float* __restrict__ kept_sum,
+                     const int32_t* __restrict__ num_copies, int64_t num_tokens, int32_t num_experts, int64_t capacity,
+                     int32_t* __restrict__ token_of_copy, int32_t* __restrict__ expert_of_copy,
+                     float* __restrict__ weight_of_copy) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (int64_t t = warp_id; t < num_tokens; t += warps) {
+    int64_t out = offsets[t];
+    const float sum = kept_sum[t];
+    for (int32_t e0 = 0; e0 < num_experts; e0 += 32) {
+      const int32_t e = e0 + lane;
+      const bool kept = e < num_experts && keep[t * num_experts + e] != 0;
+      const unsigned mask = __ballot_sync(0xffffffffu, kept);
+      const int64_t mine = out + __popc(mask & ((1u << lane) - 1u));
+      if (kept && mine < capacity) {
+        token_of_copy[mine] = static_cast<int32_t>(t);
+        expert_of_copy[mine] = e;
+        weight_of_copy[mine] = __ldg(scores + t * num_experts + e) / sum;
       }
-      ++out;
+      out += __popc(mask);
     }
   }
-  // Unused tail of the worst-case sized list: expert -1 (skipped by routing), weight 0.
-  for (int64_t i = total + threadIdx.x; i < capacity; i += kEmitThreads) {
+  const int64_t first_unused = *num_copies;
+  for (int64_t i = first_unused + warp_id * 32 + lane; i < capacity; i += warps * 32) {
     token_of_copy[i] = 0;
     expert_of_copy[i] = -1;
     weight_of_copy[i] = 0.0f;
   }
-  if (threadIdx.x == 0) *num_copies = static_cast<int32_t>(total < capacity ? total : capacity);
 }
 
 }  // namespace
@@ -240,9 +288,9 @@ int64_t sb_token_rounding_capacity(int64_t num_tokens, int32_t num_experts, int3
 
 size_t sb_token_rounding_workspace_bytes(int64_t num_tokens, int32_t num_experts, int32_t k) {
   if (num_tokens <= 0 || num_experts <= 0 || k <= 0) return 0;
-  // picks [T*k] int32 | counts [E] int32 | keep [T*E] bytes
-  const size_t ints = static_cast<size_t>(num_tokens) * k + static_cast<size_t>(num_experts);
-  return ints * sizeof(int32_t) + static_cast<size_t>(num_tokens) * num_experts;
+  // picks [T*k] int32 | counts [E] int32 | kept_per_token [T] int32 | kept_sum [T] fp32 | keep [T*E] bytes
+  const size_t words = static_cast<size_t>(num_tokens) * k + static_cast<size_t>(num_experts) + 2 * static_cast<size_t>(num_tokens);
+  return words * sizeof(int32_t) + static_cast<size_t>(num_tokens) * num_experts;
 }
 
 int sb_token_rounding(const float* scores, int64_t num_tokens, int32_t num_experts, int32_t k, int32_t tile,
@@ -261,7 +309,9 @@ int sb_token_rounding(const float* scores, int64_t num_tokens, int32_t num_exper
   const cudaStream_t s = as_stream(stream);
   int32_t* picks = static_cast<int32_t*>(workspace);
   int32_t* counts = picks + num_tokens * k;
-  uint8_t* keep = reinterpret_cast<uint8_t*>(counts + num_experts);
+  int32_t* kept_per_token = counts + num_experts;
+  float* kept_sum = reinterpret_cast<float*>(kept_per_token + num_tokens);
+  uint8_t* keep = reinterpret_cast<uint8_t*>(kept_sum + num_tokens);
   cudaError_t err = cudaMemsetAsync(counts, 0, static_cast<size_t>(num_experts) * sizeof(int32_t), s);
   if (err != cudaSuccess) return fail(SB_ERR_CUDA, "token_rounding: memset: %s", cudaGetErrorString(err));
   int64_t blocks = (num_tokens + kTopkThreads / 32 - 1) / (kTopkThreads / 32);
@@ -271,9 +321,15 @@ int sb_token_rounding(const float* scores, int64_t num_tokens, int32_t num_exper
   rounding_select_kernel<<<static_cast<unsigned>(num_experts), kSelectThreads, 0, s>>>(scores, picks, counts, num_tokens,
                                                                                       num_experts, k, tile, keep);
   if (int rc = check_launch("token_rounding (select)")) return rc;
-  rounding_emit_kernel<<<1, kEmitThreads, 0, s>>>(scores, keep, num_tokens, num_experts,
-                                                  sb_token_rounding_capacity(num_tokens, num_experts, k, tile),
-                                                  token_of_copy, expert_of_copy, weight_of_copy, num_copies);
+  const int64_t capacity = sb_token_rounding_capacity(num_tokens, num_experts, k, tile);
+  rounding_count_kernel<<<static_cast<unsigned>(blocks), kTopkThreads, 0, s>>>(scores, keep, num_tokens, num_experts,
+                                                                              kept_per_token, kept_sum);
+  if (int rc = check_launch("token_rounding (count)")) return rc;
+  rounding_scan_kernel<<<1, kEmitThreads, 0, s>>>(kept_per_token, num_tokens, capacity, num_copies);
+  if (int rc = check_launch("token_rounding (scan)")) return rc;
+  rounding_emit_kernel<<<static_cast<unsigned>(blocks), kTopkThreads, 0, s>>>(scores, keep, kept_per_token, kept_sum,
+                                                                             num_copies, num_tokens, num_experts, capacity,
+                                                                             token_of_copy, expert_of_copy, weight_of_copy);
   return check_launch("token_rounding (emit)");
 }
 

@@ -95,14 +95,14 @@ struct IndexSource {
   }
 };
 
-constexpr int kLogitsPerLane = 8;  // fused router: up to 256 experts
 constexpr int kRouterMaxK = 8;
 
-__device__ __forceinline__ bool logit_ranks_before(float a, int32_t ia, float b, int32_t ib) {
+__device__ __forceinline__ bool logit_ranks_before(float a, float b) {
+  // a strictly before b in torch.topk's order: NaN above everything, then the larger value. Equal values keep
+  // the order they were met in (the lower expert id first).
   const bool an = a != a, bn = b != b;
   if (an != bn) return an;
-  if (!an && a != b) return a > b;
-  return ia < ib;
+  return !an && a > b;
 }
 
 template <typename logit_t>
@@ -118,6 +118,9 @@ struct LogitSource {
   static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+  // A 32-copy step holds 32 / k whole tokens. Lane j < 32 / k owns token j of the step: it walks the token's E
+  // logits once and keeps the k best in registers (insertion into a short sorted list), so the tokens of a step
+  // are done side by side instead of one after the other; a shuffle then hands every copy's lane its expert id.
   template <int kIters>
   __device__ __forceinline__ bool load(int64_t begin, int64_t end, int lane, int32_t (&ids)[kIters]) const {
     const int tokens_per_step = 32 / k;
@@ -125,54 +128,57 @@ struct LogitSource {
     for (int it = 0; it < kIters; ++it) {
       ids[it] = -1;
       const int64_t step_begin = begin + it * 32;
-      for (int j = 0; j < tokens_per_step; ++j) {
-        const int64_t first_copy = step_begin + static_cast<int64_t>(j) * k;
-        if (first_copy >= end) break;  // uniform across the warp
-        const int64_t t = first_copy / k;
-        const logit_t* row = logits + t * num_experts;
-        float v[kLogitsPerLane];
+      if (step_begin >= end) continue;  // uniform across the warp
+      const int64_t first_copy = step_begin + static_cast<int64_t>(lane) * k;
+      const bool owner = lane < tokens_per_step && first_copy < end;
+      float best[kRouterMaxK];
+      int32_t best_id[kRouterMaxK];
 #pragma unroll
-        for (int q = 0; q < kLogitsPerLane; ++q) {
-          const int e = lane + 32 * q;
-          v[q] = e < num_experts ? to_float(__ldg(row + e)) : 0.0f;
-        }
-        uint32_t retired = 0;
-        float top = 0.0f, mine = 0.0f, denom = 0.0f;
-        int32_t mine_id = 0;
-        for (int r = 0; r < k; ++r) {
-          float best = -INFINITY;
-          int32_t best_id = INT32_MAX;
+      for (int r = 0; r < kRouterMaxK; ++r) {
+        best[r] = -INFINITY;
+        best_id[r] = -1;
+      }
+      if (owner) {
+        const logit_t* row = logits + (first_copy / k) * num_experts;
+        for (int32_t e = 0; e < num_experts; ++e) {
+          float v = to_float(__ldg(row + e));
+          int32_t id = e;
+          // Insert (v, id) into the list of the k best so far: it goes in front of the first entry it strictly
+          // beats (equal values stay behind the earlier, lower id), everything from there on moves down one
+          // place, and what falls off the end is dropped.
+          bool shifting = false;
 #pragma unroll
-          for (int q = 0; q < kLogitsPerLane; ++q) {
-            const int32_t e = lane + 32 * q;
-            if (e < num_experts && !((retired >> q) & 1u) && logit_ranks_before(v[q], e, best, best_id)) {
-              best = v[q];
-              best_id = e;
+          for (int r = 0; r < kRouterMaxK; ++r) {
+            if (r < k && (shifting || best_id[r] < 0 || logit_ranks_before(v, best[r]))) {
+              shifting = true;
+              const float tv = best[r];
+              const int32_t ti = best_id[r];
+              best[r] = v;
+              best_id[r] = id;
+              v = tv;
+              id = ti;
             }
           }
+        }
+        float denom = 0.0f;
 #pragma unroll
-          for (int d = 16; d > 0; d >>= 1) {
-            const float other = __shfl_xor_sync(kFullMask, best, d);
-            const int32_t other_id = __shfl_xor_sync(kFullMask, best_id, d);
-            if (logit_ranks_before(other, other_id, best, best_id)) {
-              best = other;
-              best_id = other_id;
-            }
-          }
-          if ((best_id & 31) == lane) retired |= 1u << (best_id >> 5);
-          if (r == 0) top = best;
-          denom += __expf(best - top);
-          if (lane == j * k + r) {  // the lane that carries this copy through the sort
-            ids[it] = best_id;
-            mine = best;
-            mine_id = best_id;
+        for (int r = 0; r < kRouterMaxK; ++r)
+          if (r < k) denom += __expf(best[r] - best[0]);
+#pragma unroll
+        for (int r = 0; r < kRouterMaxK; ++r) {
+          if (r < k) {
+            expert_idx[first_copy + r] = best_id[r];
+            store(expert_weight + first_copy + r, __expf(best[r] - best[0]) / denom);
           }
         }
-        if (lane >= j * k && lane < (j + 1) * k) {
-          const int64_t c = first_copy + (lane - j * k);
-          expert_idx[c] = mine_id;
-          store(expert_weight + c, __expf(mine - top) / denom);
-        }
+      }
+      // Copy `lane` of the step belongs to token lane / k, pick lane % k: fetch it from the owner's registers.
+      const int src = lane / k;
+      const int pick = lane - src * k;
+#pragma unroll
+      for (int r = 0; r < kRouterMaxK; ++r) {
+        const int32_t from_owner = __shfl_sync(kFullMask, best_id[r], src);
+        if (r == pick && step_begin + lane < end) ids[it] = from_owner;
       }
     }
     return false;
@@ -712,12 +718,12 @@ int launch_route(const index_t* expert_idx, int64_t n, int32_t k, int32_t num_ex
   return check_launch("routing (scatter + layout)");
 }
 
-// Router + routing in one cluster launch. Only where a 32-copy step holds whole tokens (k a power of two),
-// a lane holds a token's logits in 8 registers (E <= 256) and the runs stay short (T*k <= 32768).
+// Router + routing in one cluster launch. Only where a 32-copy step holds whole tokens (k a power of two) and
+// the runs stay short (T*k <= 32768); any number of experts the routing kernel takes.
 constexpr int64_t kFusedRouterMaxCopies = static_cast<int64_t>(kMaxClusterBlocks) * kClusterThreads * 4;
 
 bool fused_router_fits(int64_t n_copies, int32_t k, int32_t num_experts) {
-  return n_copies <= kFusedRouterMaxCopies && num_experts <= 32 * kLogitsPerLane && k >= 1 && k <= kRouterMaxK &&
+  return n_copies <= kFusedRouterMaxCopies && num_experts <= kMaxExperts && k >= 1 && k <= kRouterMaxK &&
          (k & (k - 1)) == 0;
 }
 
@@ -856,7 +862,7 @@ int sb_route_from_logits(const void* logits, int logits_dtype, int64_t num_token
     return sb::fail(SB_ERR_UNSUPPORTED,
                     "route_from_logits: the one-launch form needs k in {1, 2, 4, 8}, E <= %d and T*k <= %lld; "
                     "use sb_router_topk followed by sb_route",
-                    32 * sb::kLogitsPerLane, (long long)sb::kFusedRouterMaxCopies);
+                    sb::kMaxExperts, (long long)sb::kFusedRouterMaxCopies);
   int64_t want_rb = 0;
   if (int rc = sb_route_sizes(num_tokens * k, num_experts, static_cast<int64_t>(ffn_blocks) * block_size, block_size,
                               &want_rb, nullptr, nullptr))

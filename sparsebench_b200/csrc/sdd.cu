@@ -61,6 +61,7 @@ int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const in
   // so that a W1 tile is read from HBM once per band instead of once per wave (measured on the
   // Mixtral-like shape: 1027 -> 861 us; shapes with ~2 row blocks per expert lose 3-5 % and stay plain).
   params.raster_rows = num_row_blocks >= 4 * num_experts ? 8 : 1;
+  params.reuse_weights = weights_reused_in_l2(num_row_blocks, num_experts) ? 1 : 0;
   if (dispatch == nullptr && use_pair_kernel(padded_offsets, num_row_blocks, num_experts)) {
     params.raster_rows = 4;  // bands of 4 pairs = 8 row blocks
     return launch_gemm_pair<GemmOp::kSdd>(map_a, map_a, map_b, map_out, params, padded_offsets, num_experts,
