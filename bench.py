@@ -151,64 +151,62 @@ class ClockSampler:
 
 
 def pipelined_e2e_ms(forward, host_inputs, weights, warmup: int, steps: int) -> float:
-    """ms per step of `forward` fed from pinned HOST buffers when consecutive steps overlap the way a
-    serving loop runs them: step i+1's inputs are copied in while step i computes and step i-1's
-    result is copied out (three streams, two sets of device buffers, the layer of each set captured
-    once as a CUDA graph and replayed, so that the host only enqueues copies and one graph launch per
-    step). Every step's host->device and device->host copies are inside the timed region; the
-    weights (1 GB, far larger than L2) are re-streamed from HBM by every step."""
+    """ms per step of `forward` fed from pinned HOST buffers when consecutive steps overlap the way a serving loop
+    runs them: while step i computes, step i+1's inputs are copied in and step i-1's result is copied out. Two sets
+    of device buffers; one CUDA graph per set whose three branches are exactly those three things (the copy-in of
+    the OTHER set, this set's layer, the copy-out of the other set's result), so a step is ONE graph launch and the
+    host enqueues nothing else. Every step's host->device and device->host copies are inside the timed region; the
+    expert weights (far larger than L2) are re-streamed from HBM by every step."""
     host_x, host_idx, host_w = host_inputs
     device = weights[0].device
-    copy_in, compute, copy_out = (torch.cuda.Stream(device) for _ in range(3))
+    main, side_in, side_out = (torch.cuda.Stream(device) for _ in range(3))
     sets = []
     for _ in range(2):
-        b = {
+        sets.append({
             "x": torch.empty(host_x.shape, dtype=host_x.dtype, device=device),
             "idx": torch.empty(host_idx.shape, dtype=host_idx.dtype, device=device),
             "w": torch.empty(host_w.shape, dtype=host_w.dtype, device=device),
-            "out": torch.empty(host_x.shape, dtype=host_x.dtype).pin_memory(),
-            "loaded": torch.cuda.Event(), "computed": torch.cuda.Event(), "copied": torch.cuda.Event(),
-        }
+            "result": torch.empty(host_x.shape, dtype=host_x.dtype, device=device),
+            "host_out": torch.empty(host_x.shape, dtype=host_x.dtype).pin_memory(),
+        })
+    for b in sets:
         b["x"].copy_(host_x)
         b["idx"].copy_(host_idx)
         b["w"].copy_(host_w)
-        torch.cuda.synchronize(device)
-        with torch.cuda.stream(compute):
-            forward(b["x"], b["idx"], b["w"], *weights)  # one-time set-up outside the capture
-        torch.cuda.synchronize(device)
-        b["graph"] = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(b["graph"], stream=compute):
-            b["result"] = forward(b["x"], b["idx"], b["w"], *weights)
-        sets.append(b)
+    torch.cuda.synchronize(device)
+    with torch.cuda.stream(main):
+        forward(sets[0]["x"], sets[0]["idx"], sets[0]["w"], *weights)  # one-time set-up outside the captures
+    torch.cuda.synchronize(device)
+    graphs = []
+    for p in range(2):
+        mine, other = sets[p], sets[1 - p]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=main):
+            side_in.wait_stream(main)
+            side_out.wait_stream(main)
+            with torch.cuda.stream(side_in):    # the next step's inputs
+                other["x"].copy_(host_x, non_blocking=True)
+                other["idx"].copy_(host_idx, non_blocking=True)
+                other["w"].copy_(host_w, non_blocking=True)
+            with torch.cuda.stream(side_out):   # the previous step's result
+                other["host_out"].copy_(other["result"], non_blocking=True)
+            mine["result"].copy_(forward(mine["x"], mine["idx"], mine["w"], *weights))  # this step's layer
+            main.wait_stream(side_in)
+            main.wait_stream(side_out)
+        graphs.append(graph)
 
     def run(n: int) -> None:
-        for i in range(n):
-            b = sets[i % 2]
-            with torch.cuda.stream(copy_in):
-                copy_in.wait_event(b["computed"])  # the layer that last read this buffer set is done
-                b["x"].copy_(host_x, non_blocking=True)
-                b["idx"].copy_(host_idx, non_blocking=True)
-                b["w"].copy_(host_w, non_blocking=True)
-                b["loaded"].record(copy_in)
-            with torch.cuda.stream(compute):
-                compute.wait_event(b["loaded"])
-                compute.wait_event(b["copied"])  # the graph's output buffer has been read out
-                b["graph"].replay()
-                b["computed"].record(compute)
-            with torch.cuda.stream(copy_out):
-                copy_out.wait_event(b["computed"])
-                b["out"].copy_(b["result"], non_blocking=True)
-                b["copied"].record(copy_out)
+        with torch.cuda.stream(main):
+            for i in range(n):
+                graphs[i % 2].replay()
 
     torch.cuda.synchronize(device)
     run(max(warmup, 4))
     torch.cuda.synchronize(device)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record(copy_in)
+    start.record(main)
     run(steps)
-    for stream in (copy_in, compute):
-        copy_out.wait_stream(stream)
-    end.record(copy_out)
+    end.record(main)
     torch.cuda.synchronize(device)
     return start.elapsed_time(end) / steps
 
@@ -543,8 +541,9 @@ def run_single_gpu(args: argparse.Namespace) -> None:
         "clocks": clocks.summary(),
         "e2e": {"value": cfg.useful_flops / (e2e_ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms_per_step, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "how": "steps pipelined over three streams (copy in, layer as a CUDA-graph replay, copy out), two buffer "
-                       "sets; every step's H2D and D2H copies are inside the timed region",
+                "how": "steps pipelined: one CUDA-graph launch per step whose three branches are the next step's H2D copy, "
+                       "this step's layer and the previous step's D2H copy (two buffer sets); every step's copies are "
+                       "inside the timed region",
                 "single_step_latency_ms": e2e_latency_ms},
         "gpu_launches": 4 * args.steps,
         "roofline": roofline,

@@ -1,8 +1,9 @@
 """TEST/BENCH INFRASTRUCTURE, not product: builds the reference's own CUDA extension for sm_100 so
 that the reference's GPU kernels can serve as a second oracle and as a same-machine comparison row.
 
-    python oracle/build_ref_ext.py [/path/to/reference]          (default: /root/reference, else
-                                                                  baseline/_ref)
+    python oracle/build_ref_ext.py [/path/to/reference]
+    (default: $SPARSEBENCH_REFERENCE, a checkout named `reference` next to this repository, or the copy under
+    baseline/_ref)
 
 The reference's build system is not run. Its ten source files (csrc/bindings.cpp, smoke.cu,
 routing.cu, dsd.cpp, dsd_v1..v5.cu, sdd.cu: the list in its setup.py:14-25) are compiled where
@@ -28,8 +29,9 @@ SOURCES = ["bindings.cpp", "smoke.cu", "routing.cu", "dsd.cpp", "dsd_v1.cu", "ds
 
 
 def reference_csrc(arg: str | None = None) -> Path | None:
-    candidates = [Path(arg) / "csrc"] if arg else []
-    candidates += [Path("/root/reference/csrc"), Path(__file__).resolve().parent.parent / "baseline" / "_ref" / "csrc"]
+    root = Path(__file__).resolve().parent.parent
+    named = [arg, os.environ.get("SPARSEBENCH_REFERENCE"), root.parent / "reference", root / "baseline" / "_ref"]
+    candidates = [Path(c) / "csrc" for c in named if c]
     for c in candidates:
         if (c / "bindings.cpp").exists():
             return c
