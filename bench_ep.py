@@ -321,7 +321,7 @@ def run_owner_profile(args) -> None:
         tokens = make_layer(cfg, seed=0, token_seed=rank, experts=range(0)).to(device)
         _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(tokens.expert_idx, cfg.num_experts)
         ex.epoch[rank].fill_(1)
-        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts))
+        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts, sorted_token.numel()))
         sorts.append(sorted_token)
         xs.append(tokens.x)
     w2_cat = mine.w2.view(experts_local * cfg.ffn_dim, cfg.d_model)
@@ -485,7 +485,11 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         launches_per_step = 9 if fused_return else 10
         dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for their expert's arrival flags"
     else:
-        launches_per_step = (12 if moe.peer is not None else 8) + route_launches - (1 if fused_return else 0)
+        if moe.peer is not None:
+            # sort, plan, push counts, push rows, barrier, owner layout, SDD, DSD (+ return) [, push rows], barrier, combine
+            launches_per_step = 10 if fused_return else 11
+        else:
+            launches_per_step = 8 + route_launches
         dispatch_leg = "separate push kernel and a barrier before routing" if moe.peer is not None else "all-to-all collective"
     if moe.micro_batches > 1:
         launches_per_step = launches_per_step * moe.micro_batches + 1  # every part is a whole step, plus the concatenation

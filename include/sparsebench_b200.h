@@ -341,9 +341,9 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * the owners' tensor cores already work on what has arrived.
  *
  * sb_ep_dispatch_plan: from the source's sort by global expert (expert_offsets [E + 1]) builds the
- * push plan (4 * (N * experts_local + 1) ints): the rows of every (destination d, local expert e)
- * pair cut into chunks, pairs ordered expert-major, so that every owner receives its first experts
- * first. Also stores this rank's count of every pair into rank d's counts table
+ * push plan (sb_ep_dispatch_plan_ints(n_copies, N * experts_local) ints, 16-byte aligned): the rows of
+ * every (destination d, local expert e) pair cut into chunks of 8, pairs ordered expert-major, so that
+ * every owner receives its first experts first. Also stores this rank's count of every pair into rank d's counts table
  * peer_counts[d][my_rank * experts_local + e] (NULL: skip). Follow it with sb_ep_barrier; after the
  * barrier every owner knows how many rows to expect from whom.
  *
@@ -361,13 +361,14 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * the step, so that every rank uses the same value; flags never need clearing.
  *
  * sb_ep_sdd_dispatch: sb_sdd over the receive buffer with both sides of that protocol inside the
- * matmul kernel: four extra warps per thread block do this rank's pushes (as a source), and the
+ * matmul kernel: six extra warps per thread block do this rank's pushes (as a source), and the
  * gather warps wait, per tile, until the tile's expert has arrived from all N sources (as an owner:
  * my_flags, this rank's flag array). The wait is bounded (1 s): on expiry SB_DEV_TIMEOUT_DISPATCH is
  * OR-ed into *dev_status and the kernel winds down. recv_rows [N * capacity, D] is this rank's receive
  * buffer, row_slot the owner layout's row_token. Padding-only groups of 32 rows are not stored.
  * Every rank must launch it once per step (an owner without rows still has rows to push).
  */
+int64_t sb_ep_dispatch_plan_ints(int64_t n_copies, int32_t num_pairs);
 int sb_ep_dispatch_plan(const int32_t* expert_offsets, int32_t num_ranks, int32_t experts_local, int32_t capacity,
                         int32_t my_rank, int32_t* const* peer_counts, int32_t* plan, sb_stream_t stream);
 int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,

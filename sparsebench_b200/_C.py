@@ -458,15 +458,16 @@ def ep_barrier(peer_pads: torch.Tensor, my_pad: torch.Tensor, epoch: torch.Tenso
 # ---- dispatch overlapped with the owner's first matmul (see csrc/ep_dispatch.cuh) ----------------------
 
 def ep_dispatch_plan(expert_offsets: torch.Tensor, num_ranks: int, experts_per_rank: int, capacity: int, my_rank: int,
-                     peer_counts: torch.Tensor | None) -> torch.Tensor:
-    """The source's push plan, int32 [4 * (N * E_local + 1)], from its sort by global expert; also stores this
-    rank's per-expert counts into every destination's table (peer_counts: int64 device array of base addresses)."""
+                     peer_counts: torch.Tensor | None, n_copies: int) -> torch.Tensor:
+    """The source's push plan (int32, sb_ep_dispatch_plan_ints long) from its sort by global expert of its n_copies
+    copies; also stores this rank's per-expert counts into every destination's table (peer_counts: int64 device
+    array of base addresses)."""
     lib = _lib.load()
     _check_index(expert_offsets, "expert_offsets")
     pairs = num_ranks * experts_per_rank
     _check(expert_offsets.numel() == pairs + 1, "expert_offsets must have E + 1 entries")
     with torch.cuda.device(expert_offsets.device):
-        plan = torch.empty(4 * (pairs + 1), dtype=torch.int32, device=expert_offsets.device)
+        plan = torch.empty(lib.sb_ep_dispatch_plan_ints(n_copies, pairs), dtype=torch.int32, device=expert_offsets.device)
         _lib.check(lib.sb_ep_dispatch_plan(_ptr(expert_offsets), num_ranks, experts_per_rank, capacity, my_rank,
                                            _ptr(peer_counts) if peer_counts is not None else None, _ptr(plan), _stream()))
     return plan
@@ -501,7 +502,8 @@ def ep_push_rows_flagged(x: torch.Tensor, sorted_token: torch.Tensor, plan: torc
     _check_index(sorted_token, "sorted_token")
     _check_index(plan, "plan")
     num_ranks = peer_recv.numel()
-    _check(plan.numel() == 4 * (num_ranks * experts_per_rank + 1), "plan must come from ep_dispatch_plan for the same ranks")
+    _check(plan.numel() == lib.sb_ep_dispatch_plan_ints(sorted_token.numel(), num_ranks * experts_per_rank),
+           "plan must come from ep_dispatch_plan for the same ranks and copies")
     _check(done.numel() >= num_ranks * experts_per_rank, "done needs one counter per (destination, expert) pair")
     with torch.cuda.device(x.device):
         _lib.check(lib.sb_ep_push_rows_flagged(_ptr(x), _ptr(sorted_token), _ptr(plan), _ptr(peer_recv), _ptr(peer_flags),
@@ -533,7 +535,8 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
     _check(d_model % 64 == 0 and ffn_dim % 256 == 0, "need D a multiple of 64 and F a multiple of 256")
     _check(row_slot.numel() == num_row_blocks * BLOCK and num_nnz == num_row_blocks * (ffn_dim // BLOCK),
            "the layout does not match block size 128")
-    _check(plan.numel() == 4 * (num_ranks * experts_local + 1), "plan must come from ep_dispatch_plan for the same ranks")
+    _check(plan.numel() == lib.sb_ep_dispatch_plan_ints(sorted_token.numel(), num_ranks * experts_local),
+           "plan must come from ep_dispatch_plan for the same ranks and copies")
     _check(my_flags.numel() >= num_ranks * experts_local and done.numel() >= num_ranks * experts_local,
            "flags and counters need ranks * local experts entries")
     with torch.cuda.device(recv.device):

@@ -19,7 +19,7 @@
 //               instruction moves four whole 128-byte row segments. Padding rows use the zero-fill
 //               form (no global read). An asynchronous mbarrier arrive reports completion, so the
 //               threads run the full pipeline depth ahead without ever waiting for their data.
-//   warps 14-17 expert-parallel dispatch instance of SDD only (kDispatch): this rank's pushes as a source
+//   warps 14-19 expert-parallel dispatch instance of SDD only (kDispatch): this rank's pushes as a source
 //               of token rows, while the gather warps first wait, per tile, for the tile's expert to
 //               have arrived from every source rank (ep_dispatch.cuh).
 //
@@ -100,7 +100,7 @@ struct GemmConfig {
   static constexpr int kGatherWarps = kOp == GemmOp::kSdd ? 4 : 0;
   static constexpr int kFirstEpilogueWarp = 2;
   static constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
-  static constexpr int kPushWarps = kDispatch ? 4 : 0;
+  static constexpr int kPushWarps = kDispatch ? 6 : 0;
   static constexpr int kFirstPushWarp = kFirstGatherWarp + kGatherWarps;
   static constexpr int kThreads = 32 * (kFirstPushWarp + kPushWarps);
   static_assert(!kDispatch || kOp == GemmOp::kSdd, "only SDD has a dispatch instance");
@@ -546,7 +546,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     ptx::cp_async_wait_all();
   } else if (kDispatch) {
     // ---------------------------------------------------------------- dispatch pushes (this rank as a source)
-    // Chunk c of the push plan goes to worker c mod (4 * grid): consecutive chunks to different thread
+    // Chunk c of the push plan goes to worker c mod (6 * grid): consecutive chunks to different thread
     // blocks, so that the pairs every owner needs first are complete first. These warps wait for
     // nothing and run to the end of their list even if another role of the block has given up.
     const int push_warp = warp - Cfg::kFirstPushWarp;

@@ -184,8 +184,8 @@ __global__ void ep_barrier_kernel(uint32_t* const* __restrict__ peer_pads, uint3
 }
 
 // One block, one thread per (local expert e, destination d) pair, pair index q = e * N + d: the
-// expert-major order the rows are pushed in. Writes the four plan arrays (ep_dispatch.cuh) and stores
-// this rank's count of every pair into the destination's table at [my_rank][e].
+// expert-major order the rows are pushed in. Writes the plan (ep_dispatch.cuh: four per-pair arrays and one record
+// per chunk) and stores this rank's count of every pair into the destination's table at [my_rank][e].
 constexpr int kPlanThreads = 1024;
 __global__ void __launch_bounds__(kPlanThreads, 1)
 ep_dispatch_plan_kernel(const int32_t* __restrict__ expert_offsets, int32_t num_ranks, int32_t experts_local,
@@ -230,6 +230,13 @@ ep_dispatch_plan_kernel(const int32_t* __restrict__ expert_offsets, int32_t num_
     plan[(pairs + 1) + q] = first;
     plan[2 * (pairs + 1) + q] = begin_slot;
     plan[3 * (pairs + 1) + q] = rows;
+    // The pair's chunk records, in push order.
+    int4* table = reinterpret_cast<int4*>(plan + (4 * (pairs + 1) + 3) / 4 * 4);
+    for (int32_t i = 0; i < chunks; ++i) {
+      const int32_t j0 = i * kPushChunkRows;
+      const int32_t n = max(0, min(kPushChunkRows, rows - j0));
+      table[before + i] = make_int4(first + j0, my_rank * capacity + begin_slot + j0, q, n | (chunks << 8));
+    }
   }
   if (q == pairs - 1) plan[pairs] = before + chunks;
 }
@@ -320,11 +327,17 @@ int sb_ep_push_rows(const void* src, const int32_t* index, void* const* peer_bas
   return check_launch("ep_push_rows");
 }
 
+int64_t sb_ep_dispatch_plan_ints(int64_t n_copies, int32_t num_pairs) {
+  if (n_copies <= 0 || num_pairs <= 0) return 0;
+  return sb::push_plan_ints(n_copies, num_pairs);
+}
+
 int sb_ep_dispatch_plan(const int32_t* expert_offsets, int32_t num_ranks, int32_t experts_local, int32_t capacity,
                         int32_t my_rank, int32_t* const* peer_counts, int32_t* plan, sb_stream_t stream) {
   using namespace sb;
   clear_error();
   if (!expert_offsets || !plan) return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: NULL buffer");
+  if (!aligned16(plan)) return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: plan must be 16-byte aligned");
   if (num_ranks <= 0 || experts_local <= 0 || static_cast<int64_t>(num_ranks) * experts_local > kPlanThreads ||
       capacity <= 0 || my_rank < 0 || my_rank >= num_ranks)
     return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: need 0 <= rank < ranks, ranks * local experts <= %d, capacity > 0",

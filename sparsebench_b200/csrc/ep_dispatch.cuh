@@ -25,14 +25,28 @@
 
 namespace sb {
 
-constexpr int kPushChunkRows = 4;
+constexpr int kPushChunkRows = 8;
+
+// Upper bound of the chunks in a push plan: every (destination, expert) pair may end in a partial chunk, and an
+// empty pair still has one (it only signals).
+__host__ __device__ inline int64_t push_plan_max_chunks(int64_t n_copies, int32_t num_pairs) {
+  return (n_copies + kPushChunkRows - 1) / kPushChunkRows + num_pairs;
+}
+// Ints in a push plan: four arrays of num_pairs + 1, then one int4 per chunk (16-byte aligned).
+__host__ __device__ inline int64_t push_plan_ints(int64_t n_copies, int32_t num_pairs) {
+  const int64_t head = (4 * static_cast<int64_t>(num_pairs + 1) + 3) / 4 * 4;
+  return head + 4 * push_plan_max_chunks(n_copies, num_pairs);
+}
 
 struct DispatchParams {
   // Source side.
   const uint4* x;                // [T, D] this rank's token rows
   const int32_t* sorted_token;   // [T*k] token of every sorted position (sort by global expert)
-  // Push plan, four arrays of num_pairs + 1 ints back to back, pair q = e * num_ranks + d:
+  // Push plan, pair q = e * num_ranks + d. Four arrays of num_pairs + 1 ints back to back:
   //   chunk_prefix | first_pos (sorted position of the run) | slot_start (first slot i at d) | kept (rows)
+  // then (at the next multiple of four ints) one int4 per chunk, in the order the chunks are pushed:
+  //   x = sorted position of its first row, y = its first row in the destination's buffer,
+  //   z = pair q, w = rows (low 8 bits) | chunks of the pair << 8.
   const int32_t* plan;
   uint4* const* peer_recv;       // [N] every rank's receive buffer [N * capacity, D]
   uint32_t* const* peer_flags;   // [N] every rank's arrival flags [N * E_local]
@@ -79,41 +93,34 @@ __device__ __forceinline__ void copy_row_warp(const uint4* __restrict__ src, uin
   }
 }
 
-// One warp's share of the source side: chunks worker, worker + num_workers, ... of the push plan.
+// One warp's share of the source side: chunks worker, worker + num_workers, ... of the push plan. A chunk is one
+// 16-byte record away (no search), its rows' tokens come with one coalesced load, and a row's loads are all in
+// flight before its stores: what is left per chunk is one memory latency per row and one system fence.
 __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker, int num_workers, int lane) {
   const int32_t pairs = dp.num_pairs;
-  const int32_t* chunk_prefix = dp.plan;
-  const int32_t* first_pos = dp.plan + (pairs + 1);
-  const int32_t* slot_start = dp.plan + 2 * (pairs + 1);
-  const int32_t* kept = dp.plan + 3 * (pairs + 1);
-  const int32_t total = __ldg(chunk_prefix + pairs);
+  const int32_t total = __ldg(dp.plan + pairs);  // chunk_prefix[pairs]
+  const int4* table = reinterpret_cast<const int4*>(dp.plan + (4 * (pairs + 1) + 3) / 4 * 4);
   const uint32_t epoch = *dp.epoch_word;
   for (int32_t c = worker; c < total; c += num_workers) {
-    int32_t lo = 0, hi = pairs - 1;  // last pair whose first chunk is <= c
-    while (lo < hi) {
-      const int32_t mid = (lo + hi + 1) >> 1;
-      if (__ldg(chunk_prefix + mid) <= c) lo = mid; else hi = mid - 1;
-    }
-    const int32_t q = lo;
+    const int4 chunk = __ldg(table + c);
+    const int32_t q = chunk.z;
+    const int32_t rows = chunk.w & 0xff;  // 0: the one chunk of an empty pair, which only signals
     const int32_t e = q / dp.num_ranks;
     const int32_t d = q - e * dp.num_ranks;
-    const int32_t first_chunk = __ldg(chunk_prefix + q);
-    const int32_t j0 = (c - first_chunk) * kPushChunkRows;
-    const int32_t rows = min(kPushChunkRows, __ldg(kept + q) - j0);  // <= 0: the one chunk of an empty pair
     if (rows > 0) {
-      const int32_t pos0 = __ldg(first_pos + q) + j0;
-      uint4* dst = dp.peer_recv[d] +
-                   (static_cast<int64_t>(dp.my_rank) * dp.capacity + __ldg(slot_start + q) + j0) * dp.vecs_per_row;
+      const int32_t my_token = lane < rows ? __ldg(dp.sorted_token + chunk.x + lane) : 0;
+      uint4* dst = dp.peer_recv[d] + static_cast<int64_t>(chunk.y) * dp.vecs_per_row;
       for (int32_t r = 0; r < rows; ++r) {
-        const uint4* src = dp.x + static_cast<int64_t>(__ldg(dp.sorted_token + pos0 + r)) * dp.vecs_per_row;
-        copy_row_warp(src, dst + static_cast<int64_t>(r) * dp.vecs_per_row, dp.vecs_per_row, lane);
+        const int32_t token = __shfl_sync(0xffffffffu, my_token, r);
+        copy_row_warp(dp.x + static_cast<int64_t>(token) * dp.vecs_per_row, dst + static_cast<int64_t>(r) * dp.vecs_per_row,
+                      dp.vecs_per_row, lane);
       }
       __threadfence_system();  // this lane's rows are in the destination's memory before the count below
     }
     __syncwarp();
     if (lane == 0) {
-      const int32_t chunks = __ldg(chunk_prefix + q + 1) - first_chunk;
-      if (atomicAdd(dp.done + q, 1u) + 1u == static_cast<uint32_t>(chunks)) {
+      const uint32_t chunks = static_cast<uint32_t>(chunk.w) >> 8;
+      if (atomicAdd(dp.done + q, 1u) + 1u == chunks) {
         dp.done[q] = 0u;          // ready for the next step
         __threadfence_system();   // the other chunks' rows (fenced before their counts) before the flag
         st_release_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.experts_local + e, epoch);

@@ -114,11 +114,11 @@ class CudaOps:
 
         _C.ep_barrier(peer_pads, my_pad, epoch, my_rank, status)
 
-    def dispatch_plan(self, expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts):
+    def dispatch_plan(self, expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts, n_copies):
         """The source's push plan; also stores this rank's counts into every owner's table."""
         from sparsebench_b200 import _C
 
-        return _C.ep_dispatch_plan(expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts)
+        return _C.ep_dispatch_plan(expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts, n_copies)
 
     def owner_layout(self, recv_counts: torch.Tensor, capacity: int, ffn_dim: int):
         """The owner's layout over its receive slots from the exchanged counts alone."""
@@ -368,8 +368,14 @@ class ExpertParallelMoE:
         if after_dispatch is not None:
             after_dispatch()
         mark("dispatch all-to-all")
-        slot_expert = ops.slot_experts(peer.counts, capacity)
-        topo = ops.route(slot_expert.view(-1, 1), self.experts_local, self.ffn_dim, BLOCK_SIZE)
+        if hasattr(ops, "owner_layout"):
+            # The owner's layout from the exchanged counts alone, one launch (the same arrays as slot experts +
+            # routing over the N * C mostly empty receive slots).
+            slot_expert = None
+            topo = ops.owner_layout(peer.counts, capacity, self.ffn_dim)
+        else:
+            slot_expert = ops.slot_experts(peer.counts, capacity)
+            topo = ops.route(slot_expert.view(-1, 1), self.experts_local, self.ffn_dim, BLOCK_SIZE)
         mark("routing")
         h = ops.sdd(peer.recv, self.w1, topo)
         mark("SDD + GELU (fused)")
@@ -395,7 +401,8 @@ class ExpertParallelMoE:
         ops = self.ops
         _, offsets, sorted_token, _ = source_sort
         x = x.contiguous()
-        plan = ops.dispatch_plan(offsets, self.world, self.experts_local, capacity, self.rank, peer.peer_counts)
+        plan = ops.dispatch_plan(offsets, self.world, self.experts_local, capacity, self.rank, peer.peer_counts,
+                                 sorted_token.numel())
         ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)  # counts only: nothing heavy to wait for
         mark("dispatch all-to-all")
         topo = ops.owner_layout(peer.counts, capacity, self.ffn_dim)

@@ -109,3 +109,28 @@ class CpuOps:
         rows = y[copy_row.long().clamp(min=0)].view(num_tokens, k, -1)
         rows = rows * (copy_row >= 0).view(num_tokens, k, 1)
         return (rows.float() * expert_weight.float()[..., None]).sum(dim=1)
+
+
+def dispatch_plan(offsets: np.ndarray, num_ranks: int, experts_per_rank: int, capacity: int, my_rank: int,
+                  chunk_rows: int = 8):
+    """numpy restatement of sb_ep_dispatch_plan: (chunk_prefix [pairs+1], first_pos, slot_start, kept [pairs],
+    chunk records [total, 4]) with pair q = e * N + d, the order the rows are pushed in."""
+    pairs = num_ranks * experts_per_rank
+    prefix = np.zeros(pairs + 1, dtype=np.int64)
+    first_pos, slot_start, kept = (np.zeros(pairs, dtype=np.int64) for _ in range(3))
+    records = []
+    for q in range(pairs):
+        e, d = divmod(q, num_ranks)
+        g = d * experts_per_rank + e
+        first = int(offsets[g])
+        count = int(offsets[g + 1]) - first
+        in_run = first - int(offsets[d * experts_per_rank])
+        begin = min(capacity, in_run)
+        rows = min(capacity, in_run + count) - begin
+        chunks = max(1, -(-rows // chunk_rows))
+        first_pos[q], slot_start[q], kept[q] = first, begin, rows
+        prefix[q + 1] = prefix[q] + chunks
+        for i in range(chunks):
+            n = max(0, min(chunk_rows, rows - i * chunk_rows))
+            records.append((first + i * chunk_rows, my_rank * capacity + begin + i * chunk_rows, q, n | (chunks << 8)))
+    return prefix, first_pos, slot_start, kept, np.array(records, dtype=np.int64).reshape(-1, 4)

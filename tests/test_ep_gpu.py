@@ -219,6 +219,28 @@ def test_owner_layout_from_counts_equals_routing_of_the_slots(ranks: int, expert
         assert np.array_equal(a.cpu().numpy(), getattr(oracle, name)), name
 
 
+@pytest.mark.parametrize(("num_tokens", "num_experts", "ranks", "capacity"),
+                         [(300, 8, 2, 600), (300, 8, 4, 40), (4096, 128, 8, 8192), (1, 4, 2, 8)])
+def test_dispatch_plan_matches_the_restatement(num_tokens: int, num_experts: int, ranks: int, capacity: int) -> None:
+    from sparsebench_b200 import _C
+
+    idx = routing_case("zipf", num_tokens, num_experts, seed=4)
+    _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx.cuda(), num_experts)
+    per_rank = num_experts // ranks
+    pairs = num_experts
+    for my_rank in (0, ranks - 1):
+        plan = _C.ep_dispatch_plan(offsets, ranks, per_rank, capacity, my_rank, None, sorted_token.numel()).cpu().numpy()
+        prefix, first_pos, slot_start, kept, records = ep_cpu_ops.dispatch_plan(offsets.cpu().numpy(), ranks, per_rank,
+                                                                                capacity, my_rank)
+        assert np.array_equal(plan[: pairs + 1], prefix)
+        assert np.array_equal(plan[pairs + 1: 2 * pairs + 1], first_pos)
+        assert np.array_equal(plan[2 * (pairs + 1): 2 * (pairs + 1) + pairs], slot_start)
+        assert np.array_equal(plan[3 * (pairs + 1): 3 * (pairs + 1) + pairs], kept)
+        head = (4 * (pairs + 1) + 3) // 4 * 4
+        assert np.array_equal(plan[head: head + 4 * len(records)].reshape(-1, 4), records)
+        assert len(records) <= (sorted_token.numel() + 7) // 8 + pairs
+
+
 class LocalExchange:
     """The exchange buffers of `ranks` virtual ranks, all in this GPU's memory: what PeerExchange maps across
     GPUs, for tests that run one rank's kernels at a time (no two launches ever wait for each other)."""
@@ -267,7 +289,7 @@ def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_every_flag(ra
         _C.ep_push_rows(x, send_index, old.peer_recv, rank, capacity)
         view = new.of(rank)
         view.epoch.fill_(7)
-        plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, new.peer_counts)
+        plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, new.peer_counts, sorted_token.numel())
         _C.ep_push_rows_flagged(x, sorted_token, plan, new.peer_recv, new.peer_flags, view.done, view.epoch, rank,
                                 experts_local, capacity)
         torch.cuda.synchronize()
@@ -275,7 +297,7 @@ def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_every_flag(ra
         pairs = ranks * experts_local
         chunk_prefix, kept = plan[: pairs + 1].cpu(), plan[3 * (pairs + 1): 3 * (pairs + 1) + pairs].cpu()
         assert int(kept.sum().item()) == int((send_index >= 0).sum().item())
-        assert torch.equal(chunk_prefix[1:] - chunk_prefix[:-1], torch.clamp((kept + 3) // 4, min=1).to(torch.int32))
+        assert torch.equal(chunk_prefix[1:] - chunk_prefix[:-1], torch.clamp((kept + 7) // 8, min=1).to(torch.int32))
     assert torch.equal(new.recv, old.recv)
     assert torch.equal(new.counts, old.counts)
     assert bool((new.flags == 7).all()), "every (source, expert) flag at every owner carries the epoch"
@@ -326,7 +348,7 @@ def test_two_virtual_ranks_overlapped_dispatch_matches_oracle() -> None:
     for rank in range(ranks):
         ex.epoch[rank].fill_(3)
         _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idxs[rank].cuda(), num_experts)
-        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts))
+        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts, sorted_token.numel()))
         sorts.append(sorted_token)
     x_dev = [x.cuda() for x in xs]
     view1 = ex.of(1)
@@ -374,7 +396,7 @@ def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers
     _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx, num_experts)
     view = ex.of(0)
     view.epoch.fill_(1)
-    plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, 0, ex.peer_counts)
+    plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, 0, ex.peer_counts, sorted_token.numel())
     view.counts[1] = view.counts[0]  # pretend rank 1 announced rows that never come
     topo = DeviceTopology(128, experts_local, ffn_dim // 128, *_C.ep_owner_layout(view.counts, capacity, ffn_dim))
     status = _C.device_status(torch.device("cuda", torch.cuda.current_device()))
