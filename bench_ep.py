@@ -276,13 +276,14 @@ class LocalExchange:
     multi-rank command). of(r) has the attribute names of sparsebench_b200.ep.PeerExchange."""
 
     def __init__(self, ranks: int, capacity: int, d_model: int, experts_local: int, device: torch.device) -> None:
+        segments = (capacity + 255) // 256  # arrival flags per rank pair (sb_ep_dispatch_segments)
         self.recv = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=device)
         self.ret = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=device)
         self.counts = torch.zeros(ranks, ranks, experts_local, dtype=torch.int32, device=device)
         self.pad = torch.zeros(ranks, ranks, dtype=torch.int32, device=device)
-        self.flags = torch.zeros(ranks, ranks * experts_local, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(ranks, ranks * segments, dtype=torch.int32, device=device)
         self.epoch = [torch.zeros(1, dtype=torch.int32, device=device) for _ in range(ranks)]
-        self.done = [torch.zeros(ranks * experts_local, dtype=torch.int32, device=device) for _ in range(ranks)]
+        self.done = [torch.zeros(ranks * segments, dtype=torch.int32, device=device) for _ in range(ranks)]
 
         def table(t: torch.Tensor) -> torch.Tensor:
             return torch.tensor([t[r].data_ptr() for r in range(ranks)], dtype=torch.int64, device=device)
@@ -316,12 +317,13 @@ def run_owner_profile(args) -> None:
     capacity = int(math.ceil(3.0 * n_copies / ranks / 128.0)) * 128  # keeps the buffers near 1 GB in total
     ex = LocalExchange(ranks, capacity, cfg.d_model, experts_local, device)
     mine = make_layer(cfg, seed=0, token_seed=0, experts=range(experts_local)).to(device)
-    sorts, plans, xs = [], [], []
+    sorts, starts, xs = [], [], []
     for rank in range(ranks):
         tokens = make_layer(cfg, seed=0, token_seed=rank, experts=range(0)).to(device)
-        _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(tokens.expert_idx, cfg.num_experts)
+        counts, offsets, sorted_token, _, _ = _C.sort_copies_cuda(tokens.expert_idx, cfg.num_experts)
         ex.epoch[rank].fill_(1)
-        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts, sorted_token.numel()))
+        _C.ep_push_counts(counts, ex.peer_counts, rank, experts_local)
+        starts.append(offsets)
         sorts.append(sorted_token)
         xs.append(tokens.x)
     w2_cat = mine.w2.view(experts_local * cfg.ffn_dim, cfg.d_model)
@@ -331,13 +333,14 @@ def run_owner_profile(args) -> None:
             ex.epoch[rank].fill_(step + 1)
         for rank in range(1, ranks):
             r = ex.of(rank)
-            _C.ep_push_rows_flagged(xs[rank], sorts[rank], plans[rank], ex.peer_recv, ex.peer_flags, r.done, r.epoch, rank,
+            _C.ep_push_rows_flagged(xs[rank], sorts[rank], starts[rank], ex.peer_recv, ex.peer_flags, r.done, r.epoch, rank,
                                     experts_local, capacity)
         torch.cuda.synchronize()
-        topo = DeviceTopology(128, experts_local, cfg.ffn_dim // 128, *_C.ep_owner_layout(view.counts, capacity, cfg.ffn_dim))
+        *layout, order = _C.ep_owner_layout(view.counts, capacity, cfg.ffn_dim, arrival_order=True)
+        topo = DeviceTopology(128, experts_local, cfg.ffn_dim // 128, *layout)
         h = _C.ep_sdd_dispatch(view.recv, mine.w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
-                               topo.col_indices.numel(), xs[0], sorts[0], plans[0], ex.peer_recv, ex.peer_flags, view.flags,
-                               view.done, view.epoch, 0, capacity)
+                               topo.col_indices.numel(), xs[0], sorts[0], starts[0], order, ex.peer_recv, ex.peer_flags,
+                               view.flags, view.done, view.epoch, 0, capacity)
         _C.ep_dsd_push(h, w2_cat, topo.row_offsets, topo.col_indices, topo.row_token, ex.peer_ret, 0, capacity)
         torch.cuda.synchronize()
     status = int(_C.device_status(device).item())
@@ -481,7 +484,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     fused_return = moe.peer is not None and moe.fuse_return
     fused_dispatch = moe.peer is not None and moe.fuse_dispatch
     if fused_dispatch:
-        # sort, plan, dispatch plan (+ counts), barrier, owner layout, SDD with the pushes, DSD (+ return) [, push], barrier, combine
+        # sort, plan, push counts, barrier, owner layout, SDD with the pushes, DSD (+ return) [, push], barrier, combine
         launches_per_step = 9 if fused_return else 10
         dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for their expert's arrival flags"
     else:

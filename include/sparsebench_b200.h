@@ -340,49 +340,53 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * rows, barrier, compute", only the per-expert COUNTS are exchanged up front; the rows travel while
  * the owners' tensor cores already work on what has arrived.
  *
- * sb_ep_dispatch_plan: from the source's sort by global expert (expert_offsets [E + 1]) builds the
- * push plan (sb_ep_dispatch_plan_ints(n_copies, N * experts_local) ints, 16-byte aligned): the rows of
- * every (destination d, local expert e) pair cut into chunks of 8, pairs ordered expert-major, so that
- * every owner receives its first experts first. Also stores this rank's count of every pair into rank d's counts table
- * peer_counts[d][my_rank * experts_local + e] (NULL: skip). Follow it with sb_ep_barrier; after the
- * barrier every owner knows how many rows to expect from whom.
+ * A source's copies bound for destination rank d are one contiguous run of its sort by global expert
+ * (expert_offsets [N * experts_local + 1]); copy j of that run goes to row my_rank * capacity + j of d's
+ * receive buffer (copies past the capacity are cut, as sb_ep_plan cuts them). The rows are pushed in
+ * chunks of 8, slot-major and round-robin over the destinations, so every owner's slots fill from the
+ * front; arrival is signalled per SEGMENT of 256 slots: sb_ep_dispatch_segments(capacity) flags per
+ * rank pair. Per step: sb_ep_push_counts, sb_ep_barrier (after it every owner knows how many rows to
+ * expect from whom), sb_ep_owner_layout, sb_ep_sdd_dispatch.
  *
  * sb_ep_owner_layout: the owner's block-sparse layout over its N * capacity receive slots from those
  * counts alone (recv_counts [N][experts_local]), in one launch: the arrays sb_route writes when it is
  * handed sb_ep_slot_experts' output as a k = 1 problem, bit for bit (row_token holds receive-slot
  * indices; error is always 0). N * experts_local <= 1024. max_row_blocks as sb_route_sizes gives for
- * N * capacity copies.
+ * N * capacity copies. row_block_order (NULL: not wanted; needs max_row_blocks <= 4096): the row blocks
+ * sorted by the largest slot index (within its source's region) among their rows, ties in layout order,
+ * row blocks without rows last: the order in which their rows become complete when every source fills
+ * its slots from the front.
  *
- * sb_ep_push_rows_flagged: the source side as a kernel of its own. Every row of the plan is stored into
- * its owner's receive buffer peer_recv[d] at row my_rank * capacity + i (plain stores over NVLink); when
- * the last chunk of a (d, e) pair is in, peer_flags[d][my_rank * experts_local + e] is set to the
- * current value of *epoch_word with a system-scope release store. done: num_pairs zeroed counters
- * (left zeroed). epoch_word: the counter sb_ep_barrier advances, read AFTER the counts barrier of
- * the step, so that every rank uses the same value; flags never need clearing.
+ * sb_ep_push_rows_flagged: the source side as a kernel of its own. When the last chunk of segment g of
+ * destination d is in, peer_flags[d][my_rank * segments + g] is set to the current value of *epoch_word
+ * with a system-scope release store. done: N * segments zeroed counters (left zeroed). epoch_word:
+ * the counter sb_ep_barrier advances, read AFTER the counts barrier of the step, so that every rank
+ * uses the same value; flags never need clearing.
  *
  * sb_ep_sdd_dispatch: sb_sdd over the receive buffer with both sides of that protocol inside the
  * matmul kernel: six extra warps per thread block do this rank's pushes (as a source), and the
- * gather warps wait, per tile, until the tile's expert has arrived from all N sources (as an owner:
- * my_flags, this rank's flag array). The wait is bounded (1 s): on expiry SB_DEV_TIMEOUT_DISPATCH is
+ * gather warps wait, per tile, until the segments that hold the tile's rows have arrived (as an owner:
+ * my_flags, this rank's flag array [N * segments]). Tiles are walked in row_block_order (NULL: layout
+ * order). The wait is bounded (1 s): on expiry SB_DEV_TIMEOUT_DISPATCH is
  * OR-ed into *dev_status and the kernel winds down. recv_rows [N * capacity, D] is this rank's receive
  * buffer, row_slot the owner layout's row_token. Padding-only groups of 32 rows are not stored.
  * Every rank must launch it once per step (an owner without rows still has rows to push).
  */
-int64_t sb_ep_dispatch_plan_ints(int64_t n_copies, int32_t num_pairs);
-int sb_ep_dispatch_plan(const int32_t* expert_offsets, int32_t num_ranks, int32_t experts_local, int32_t capacity,
-                        int32_t my_rank, int32_t* const* peer_counts, int32_t* plan, sb_stream_t stream);
+int32_t sb_ep_dispatch_segments(int32_t capacity);
 int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,
                        int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
                        int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,
-                       int32_t* row_offsets, int32_t* col_indices, int32_t* error, sb_stream_t stream);
-int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const int32_t* plan, void* const* peer_recv,
-                            uint32_t* const* peer_flags, uint32_t* done, const uint32_t* epoch_word, int32_t my_rank,
-                            int32_t num_ranks, int32_t experts_local, int32_t capacity, int32_t row_bytes,
-                            sb_stream_t stream);
+                       int32_t* row_offsets, int32_t* col_indices, int32_t* row_block_order, int32_t* error,
+                       sb_stream_t stream);
+int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const int32_t* expert_offsets,
+                            void* const* peer_recv, uint32_t* const* peer_flags, uint32_t* done,
+                            const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks, int32_t experts_local,
+                            int32_t capacity, int32_t row_bytes, sb_stream_t stream);
 int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const int32_t* row_slot, const int32_t* row_block_expert,
                        const int32_t* row_offsets, void* h_blocks, int32_t d_model, int32_t ffn_dim,
-                       int32_t num_row_blocks, const void* x, const int32_t* sorted_token, const int32_t* plan,
-                       void* const* peer_recv, uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
+                       int32_t num_row_blocks, const void* x, const int32_t* sorted_token,
+                       const int32_t* expert_offsets, const int32_t* row_block_order, void* const* peer_recv,
+                       uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
                        const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks, int32_t experts_local,
                        int32_t capacity, int32_t* dev_status, sb_stream_t stream);
 

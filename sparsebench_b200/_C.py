@@ -457,25 +457,17 @@ def ep_barrier(peer_pads: torch.Tensor, my_pad: torch.Tensor, epoch: torch.Tenso
 
 # ---- dispatch overlapped with the owner's first matmul (see csrc/ep_dispatch.cuh) ----------------------
 
-def ep_dispatch_plan(expert_offsets: torch.Tensor, num_ranks: int, experts_per_rank: int, capacity: int, my_rank: int,
-                     peer_counts: torch.Tensor | None, n_copies: int) -> torch.Tensor:
-    """The source's push plan (int32, sb_ep_dispatch_plan_ints long) from its sort by global expert of its n_copies
-    copies; also stores this rank's per-expert counts into every destination's table (peer_counts: int64 device
-    array of base addresses)."""
-    lib = _lib.load()
-    _check_index(expert_offsets, "expert_offsets")
-    pairs = num_ranks * experts_per_rank
-    _check(expert_offsets.numel() == pairs + 1, "expert_offsets must have E + 1 entries")
-    with torch.cuda.device(expert_offsets.device):
-        plan = torch.empty(lib.sb_ep_dispatch_plan_ints(n_copies, pairs), dtype=torch.int32, device=expert_offsets.device)
-        _lib.check(lib.sb_ep_dispatch_plan(_ptr(expert_offsets), num_ranks, experts_per_rank, capacity, my_rank,
-                                           _ptr(peer_counts) if peer_counts is not None else None, _ptr(plan), _stream()))
-    return plan
+def ep_dispatch_segments(capacity: int) -> int:
+    """Arrival flags (and the sender's chunk counters) per rank pair: one per 256 rows of the capacity."""
+    return int(_lib.load().sb_ep_dispatch_segments(capacity))
 
 
-def ep_owner_layout(recv_counts: torch.Tensor, capacity: int, ffn_dim: int, block_size: int = BLOCK) -> list[torch.Tensor]:
+def ep_owner_layout(recv_counts: torch.Tensor, capacity: int, ffn_dim: int, block_size: int = BLOCK,
+                    arrival_order: bool = False) -> list[torch.Tensor]:
     """The owner's layout over its N * capacity receive slots from the exchanged counts [N, E_local] alone: the
-    eight arrays build_topology_cuda returns for ep_slot_experts' output, in one launch (error always 0)."""
+    eight arrays build_topology_cuda returns for ep_slot_experts' output, in one launch (error always 0). With
+    arrival_order a ninth array follows: the row blocks in the order their rows become complete when every
+    source fills its slots from the front (what ep_sdd_dispatch walks)."""
     lib = _lib.load()
     _check(recv_counts.is_cuda and recv_counts.dtype == torch.int32 and recv_counts.dim() == 2 and
            recv_counts.is_contiguous(), "recv_counts must be a contiguous [N, E_local] int32 CUDA tensor")
@@ -487,38 +479,43 @@ def ep_owner_layout(recv_counts: torch.Tensor, capacity: int, ffn_dim: int, bloc
     max_rb, max_rows, ffn_blocks = max_rb.value, max_rows.value, ffn_blocks.value
     with torch.cuda.device(recv_counts.device):
         sizes = [experts_local, experts_local + 1, max_rows, n, max_rb, max_rb + 1, max_rb * ffn_blocks, 1]
+        if arrival_order:
+            sizes.append(max_rb)
         parts = list(torch.split(torch.empty(sum(sizes), dtype=torch.int32, device=recv_counts.device), sizes))
+        order = parts.pop() if arrival_order else None
+        error = parts[7]
         _lib.check(lib.sb_ep_owner_layout(_ptr(recv_counts), num_ranks, experts_local, capacity, ffn_blocks, block_size,
-                                          max_rb, *(_ptr(t) for t in parts), _stream()))
-    return parts
+                                          max_rb, *(_ptr(t) for t in parts[:7]), _ptr(order) if arrival_order else None,
+                                          _ptr(error), _stream()))
+    return parts + [order] if arrival_order else parts
 
 
-def ep_push_rows_flagged(x: torch.Tensor, sorted_token: torch.Tensor, plan: torch.Tensor, peer_recv: torch.Tensor,
-                         peer_flags: torch.Tensor, done: torch.Tensor, epoch: torch.Tensor, my_rank: int,
-                         experts_per_rank: int, capacity: int) -> None:
+def ep_push_rows_flagged(x: torch.Tensor, sorted_token: torch.Tensor, expert_offsets: torch.Tensor,
+                         peer_recv: torch.Tensor, peer_flags: torch.Tensor, done: torch.Tensor, epoch: torch.Tensor,
+                         my_rank: int, experts_per_rank: int, capacity: int) -> None:
     """The source side of the overlapped dispatch as a kernel of its own (sb_ep_push_rows_flagged)."""
     lib = _lib.load()
     _check(x.is_cuda and x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D CUDA tensor")
     _check_index(sorted_token, "sorted_token")
-    _check_index(plan, "plan")
+    _check_index(expert_offsets, "expert_offsets")
     num_ranks = peer_recv.numel()
-    _check(plan.numel() == lib.sb_ep_dispatch_plan_ints(sorted_token.numel(), num_ranks * experts_per_rank),
-           "plan must come from ep_dispatch_plan for the same ranks and copies")
-    _check(done.numel() >= num_ranks * experts_per_rank, "done needs one counter per (destination, expert) pair")
+    _check(expert_offsets.numel() == num_ranks * experts_per_rank + 1, "expert_offsets must have E + 1 entries")
+    _check(done.numel() >= num_ranks * ep_dispatch_segments(capacity), "done needs one counter per (destination, segment)")
     with torch.cuda.device(x.device):
-        _lib.check(lib.sb_ep_push_rows_flagged(_ptr(x), _ptr(sorted_token), _ptr(plan), _ptr(peer_recv), _ptr(peer_flags),
-                                               _ptr(done), _ptr(epoch), my_rank, num_ranks, experts_per_rank, capacity,
-                                               x.shape[1] * x.element_size(), _stream()))
+        _lib.check(lib.sb_ep_push_rows_flagged(_ptr(x), _ptr(sorted_token), _ptr(expert_offsets), _ptr(peer_recv),
+                                               _ptr(peer_flags), _ptr(done), _ptr(epoch), my_rank, num_ranks,
+                                               experts_per_rank, capacity, x.shape[1] * x.element_size(), _stream()))
 
 
 def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor, row_block_expert: torch.Tensor,
                     row_offsets: torch.Tensor, num_nnz: int, x: torch.Tensor, sorted_token: torch.Tensor,
-                    plan: torch.Tensor, peer_recv: torch.Tensor, peer_flags: torch.Tensor, my_flags: torch.Tensor,
-                    done: torch.Tensor, epoch: torch.Tensor, my_rank: int, capacity: int) -> torch.Tensor:
+                    expert_offsets: torch.Tensor, row_block_order: torch.Tensor | None, peer_recv: torch.Tensor,
+                    peer_flags: torch.Tensor, my_flags: torch.Tensor, done: torch.Tensor, epoch: torch.Tensor,
+                    my_rank: int, capacity: int) -> torch.Tensor:
     """SDD + GELU over the receive buffer `recv` [N * capacity, D] whose rows are still arriving: extra warps of
     the same kernel push this rank's own rows `x[sorted_token]` to their owners, and every tile waits (bounded)
-    for its expert's rows from all sources. Returns the blocks [num_nnz, 128, 128] like sdd_cuda with
-    skip_padding_rows."""
+    for the 256-row segments its rows lie in. Tiles are walked in row_block_order (ep_owner_layout's arrival
+    order; None: layout order). Returns the blocks [num_nnz, 128, 128] like sdd_cuda with skip_padding_rows."""
     lib = _lib.load()
     _check(recv.is_cuda and w1.is_cuda and x.is_cuda and recv.device == w1.device == x.device, "all inputs on one GPU")
     _check(recv.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and x.dtype == torch.bfloat16, "rows and w1 must be bfloat16")
@@ -526,7 +523,7 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
     _check(recv.dim() == 2 and w1.dim() == 3 and x.dim() == 2 and w1.shape[1] == recv.shape[1] == x.shape[1],
            "recv and x must be [., D] and w1 [E_local, D, F]")
     for t, name in ((row_slot, "row_slot"), (row_block_expert, "row_block_expert"), (row_offsets, "row_offsets"),
-                    (sorted_token, "sorted_token"), (plan, "plan")):
+                    (sorted_token, "sorted_token"), (expert_offsets, "expert_offsets")):
         _check_index(t, name)
     experts_local, d_model, ffn_dim = w1.shape
     num_ranks = peer_recv.numel()
@@ -535,15 +532,19 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
     _check(d_model % 64 == 0 and ffn_dim % 256 == 0, "need D a multiple of 64 and F a multiple of 256")
     _check(row_slot.numel() == num_row_blocks * BLOCK and num_nnz == num_row_blocks * (ffn_dim // BLOCK),
            "the layout does not match block size 128")
-    _check(plan.numel() == lib.sb_ep_dispatch_plan_ints(sorted_token.numel(), num_ranks * experts_local),
-           "plan must come from ep_dispatch_plan for the same ranks and copies")
-    _check(my_flags.numel() >= num_ranks * experts_local and done.numel() >= num_ranks * experts_local,
-           "flags and counters need ranks * local experts entries")
+    _check(expert_offsets.numel() == num_ranks * experts_local + 1, "expert_offsets must have E + 1 entries")
+    if row_block_order is not None:
+        _check_index(row_block_order, "row_block_order")
+        _check(row_block_order.numel() == num_row_blocks, "row_block_order must have one entry per row block")
+    segments = ep_dispatch_segments(capacity)
+    _check(my_flags.numel() >= num_ranks * segments and done.numel() >= num_ranks * segments,
+           "flags and counters need ranks * ep_dispatch_segments(capacity) entries")
     with torch.cuda.device(recv.device):
         out = torch.empty((num_nnz, BLOCK, BLOCK), dtype=torch.bfloat16, device=recv.device)
         _lib.check(lib.sb_ep_sdd_dispatch(_ptr(recv), _ptr(w1), _ptr(row_slot), _ptr(row_block_expert), _ptr(row_offsets),
                                           _ptr(out), d_model, ffn_dim, num_row_blocks, _ptr(x), _ptr(sorted_token),
-                                          _ptr(plan), _ptr(peer_recv), _ptr(peer_flags), _ptr(my_flags), _ptr(done),
+                                          _ptr(expert_offsets), _ptr(row_block_order) if row_block_order is not None else None,
+                                          _ptr(peer_recv), _ptr(peer_flags), _ptr(my_flags), _ptr(done),
                                           _ptr(epoch), my_rank, num_ranks, experts_local, capacity,
                                           _ptr(device_status(recv.device)), _stream()))
     return out

@@ -212,7 +212,10 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int32_t band = tile / band_tiles;
     const int32_t first = band * p.raster_rows;
     const int32_t height = min(p.raster_rows, p.num_row_blocks - first);
-    return first + (tile - band * band_tiles) % height;
+    const int32_t position = first + (tile - band * band_tiles) % height;
+    // Dispatch instance: the walk follows the order the rows arrive in, not the order of the layout.
+    if (kDispatch && p.dispatch.row_block_order != nullptr) return __ldg(p.dispatch.row_block_order + position);
+    return position;
   };
   auto slice_of = [&](int32_t tile) {
     const int32_t band = tile / band_tiles;
@@ -493,9 +496,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       load_tokens(tile, tok);
       cur = load_tile_info(tile);
     }
-    // Dispatch instance: the expert whose rows are known to have arrived from every source, and the
-    // value the arrival flags carry in this step.
-    int32_t arrived_expert = -1;
+    // Dispatch instance: the value the arrival flags carry in this step.
     const uint32_t dispatch_epoch = kDispatch ? *p.dispatch.epoch_word : 0u;
     while (ok && tile < total_tiles) {
       // The next tile's record and row -> token table are fetched while this tile is gathered.
@@ -507,15 +508,14 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         next_info = load_tile_info(next);
       }
       const bool live = cur.begin != cur.end;
-      const int32_t expert = cur.expert;
       cur = next_info;
-      if (kDispatch && live && expert != arrived_expert) {
-        if (!wait_expert_arrived(p.dispatch, expert, dispatch_epoch, lane, abort_word)) {
+      if (kDispatch && live) {
+        // The rows of this tile (tok[] holds their receive slots) may still be on their way.
+        if (!wait_rows_arrived(p.dispatch, tok, dispatch_epoch, abort_word)) {
           if (lane == 0) give_up(SB_DEV_TIMEOUT_DISPATCH);
           break;
         }
         __syncwarp();
-        arrived_expert = expert;
       }
       if (live) {
         const __nv_bfloat16* src[8];

@@ -17,11 +17,10 @@
 // sb_gather_rows     out[j][:] = src[index[j]][:] where index[j] >= 0 (16-byte vectors).
 //
 // Dispatch overlapped with the owner's first matmul (ep_dispatch.cuh has the protocol):
-// sb_ep_dispatch_plan   the source's push plan (chunks of rows per (destination, local expert) pair,
-//                       expert-major) and its per-expert counts stored into every destination's table.
+// sb_ep_dispatch_segments  arrival flags (and chunk counters) per rank pair for a capacity.
 // sb_ep_push_rows_flagged  the source side alone, as a kernel of its own: rows into the owners'
-//                       receive buffers, one arrival flag per (source, expert) at the owner. The same
-//                       device code runs inside the SDD kernel's push warps (sb_ep_sdd_dispatch).
+//                       receive buffers, one arrival flag per (source, 256-row segment) at the owner. The
+//                       same device code runs inside the SDD kernel's push warps (sb_ep_sdd_dispatch).
 
 #include <cuda_bf16.h>
 
@@ -183,64 +182,6 @@ __global__ void ep_barrier_kernel(uint32_t* const* __restrict__ peer_pads, uint3
   if (p == 0) *epoch_word = epoch;
 }
 
-// One block, one thread per (local expert e, destination d) pair, pair index q = e * N + d: the
-// expert-major order the rows are pushed in. Writes the plan (ep_dispatch.cuh: four per-pair arrays and one record
-// per chunk) and stores this rank's count of every pair into the destination's table at [my_rank][e].
-constexpr int kPlanThreads = 1024;
-__global__ void __launch_bounds__(kPlanThreads, 1)
-ep_dispatch_plan_kernel(const int32_t* __restrict__ expert_offsets, int32_t num_ranks, int32_t experts_local,
-                        int32_t capacity, int32_t my_rank, int32_t* const* __restrict__ peer_counts,
-                        int32_t* __restrict__ plan) {
-  __shared__ int32_t warp_sums[32];
-  const int q = threadIdx.x;
-  const int lane = q & 31, warp = q >> 5;
-  const int32_t pairs = num_ranks * experts_local;
-  int32_t chunks = 0, first = 0, begin_slot = 0, rows = 0;
-  if (q < pairs) {
-    const int32_t e = q / num_ranks;
-    const int32_t d = q - e * num_ranks;
-    const int32_t g = d * experts_local + e;
-    first = expert_offsets[g];
-    const int32_t count = expert_offsets[g + 1] - first;
-    const int32_t in_run = first - expert_offsets[d * experts_local];  // rows bound for d before this expert's
-    begin_slot = min(capacity, in_run);
-    rows = min(capacity, in_run + count) - begin_slot;
-    chunks = max(1, (rows + kPushChunkRows - 1) / kPushChunkRows);  // an empty pair still has to signal
-    if (peer_counts != nullptr) peer_counts[d][my_rank * experts_local + e] = count;
-  }
-  int32_t inclusive = chunks;
-  for (int s = 1; s < 32; s <<= 1) {
-    const int32_t below = __shfl_up_sync(0xffffffffu, inclusive, s);
-    if (lane >= s) inclusive += below;
-  }
-  if (lane == 31) warp_sums[warp] = inclusive;
-  __syncthreads();
-  if (warp == 0) {
-    int32_t v = warp_sums[lane];
-    for (int s = 1; s < 32; s <<= 1) {
-      const int32_t below = __shfl_up_sync(0xffffffffu, v, s);
-      if (lane >= s) v += below;
-    }
-    warp_sums[lane] = v;
-  }
-  __syncthreads();
-  const int32_t before = (warp > 0 ? warp_sums[warp - 1] : 0) + inclusive - chunks;
-  if (q < pairs) {
-    plan[q] = before;
-    plan[(pairs + 1) + q] = first;
-    plan[2 * (pairs + 1) + q] = begin_slot;
-    plan[3 * (pairs + 1) + q] = rows;
-    // The pair's chunk records, in push order.
-    int4* table = reinterpret_cast<int4*>(plan + (4 * (pairs + 1) + 3) / 4 * 4);
-    for (int32_t i = 0; i < chunks; ++i) {
-      const int32_t j0 = i * kPushChunkRows;
-      const int32_t n = max(0, min(kPushChunkRows, rows - j0));
-      table[before + i] = make_int4(first + j0, my_rank * capacity + begin_slot + j0, q, n | (chunks << 8));
-    }
-  }
-  if (q == pairs - 1) plan[pairs] = before + chunks;
-}
-
 constexpr int kPushThreads = 256;
 __global__ void __launch_bounds__(kPushThreads)
 ep_push_rows_flagged_kernel(const DispatchParams dp) {
@@ -327,33 +268,16 @@ int sb_ep_push_rows(const void* src, const int32_t* index, void* const* peer_bas
   return check_launch("ep_push_rows");
 }
 
-int64_t sb_ep_dispatch_plan_ints(int64_t n_copies, int32_t num_pairs) {
-  if (n_copies <= 0 || num_pairs <= 0) return 0;
-  return sb::push_plan_ints(n_copies, num_pairs);
-}
+int32_t sb_ep_dispatch_segments(int32_t capacity) { return capacity > 0 ? sb::dispatch_segments(capacity) : 0; }
 
-int sb_ep_dispatch_plan(const int32_t* expert_offsets, int32_t num_ranks, int32_t experts_local, int32_t capacity,
-                        int32_t my_rank, int32_t* const* peer_counts, int32_t* plan, sb_stream_t stream) {
-  using namespace sb;
-  clear_error();
-  if (!expert_offsets || !plan) return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: NULL buffer");
-  if (!aligned16(plan)) return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: plan must be 16-byte aligned");
-  if (num_ranks <= 0 || experts_local <= 0 || static_cast<int64_t>(num_ranks) * experts_local > kPlanThreads ||
-      capacity <= 0 || my_rank < 0 || my_rank >= num_ranks)
-    return fail(SB_ERR_INVALID_ARGUMENT, "ep_dispatch_plan: need 0 <= rank < ranks, ranks * local experts <= %d, capacity > 0",
-                kPlanThreads);
-  ep_dispatch_plan_kernel<<<1, kPlanThreads, 0, as_stream(stream)>>>(expert_offsets, num_ranks, experts_local, capacity,
-                                                                      my_rank, peer_counts, plan);
-  return check_launch("ep_dispatch_plan");
-}
-
-int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const int32_t* plan, void* const* peer_recv,
+int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const int32_t* expert_offsets,
+                            void* const* peer_recv,
                             uint32_t* const* peer_flags, uint32_t* done, const uint32_t* epoch_word, int32_t my_rank,
                             int32_t num_ranks, int32_t experts_local, int32_t capacity, int32_t row_bytes,
                             sb_stream_t stream) {
   using namespace sb;
   clear_error();
-  if (!x || !sorted_token || !plan || !peer_recv || !peer_flags || !done || !epoch_word)
+  if (!x || !sorted_token || !expert_offsets || !peer_recv || !peer_flags || !done || !epoch_word)
     return fail(SB_ERR_INVALID_ARGUMENT, "ep_push_rows_flagged: NULL buffer");
   if (num_ranks <= 0 || num_ranks > 32 || experts_local <= 0 || my_rank < 0 || my_rank >= num_ranks || capacity <= 0 ||
       row_bytes <= 0 || row_bytes % 16 != 0 || !aligned16(x))
@@ -364,7 +288,7 @@ int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const in
   DispatchParams dp{};
   dp.x = static_cast<const uint4*>(x);
   dp.sorted_token = sorted_token;
-  dp.plan = plan;
+  dp.expert_offsets = expert_offsets;
   dp.peer_recv = reinterpret_cast<uint4* const*>(peer_recv);
   dp.peer_flags = peer_flags;
   dp.done = done;
@@ -373,8 +297,8 @@ int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const in
   dp.num_ranks = num_ranks;
   dp.experts_local = experts_local;
   dp.capacity = capacity;
+  dp.segments = dispatch_segments(capacity);
   dp.vecs_per_row = row_bytes / 16;
-  dp.num_pairs = num_ranks * experts_local;
   ep_push_rows_flagged_kernel<<<static_cast<unsigned>(info->sm_count * 2), kPushThreads, 0, as_stream(stream)>>>(dp);
   return check_launch("ep_push_rows_flagged");
 }

@@ -5,14 +5,19 @@
 // E_local experts. Instead of "push all rows, barrier, then compute", rows travel while the owner's
 // tensor cores already work:
 //
-//   source   walks its copies expert-major (local expert 0 of every destination first, then 1, ...),
-//            in chunks of a few rows of one (destination d, local expert e) pair; a warp stores a
-//            chunk's rows straight into d's receive buffer (plain stores through the peer mapping,
-//            i.e. over NVLink), fences, and counts the chunk; whoever completes a pair's last chunk
-//            publishes the step's epoch in d's flag [source][e] with a system-scope release store.
-//   owner    before a gather warp of SDD reads the rows of a tile of local expert e it waits, bounded,
-//            until the flags [s][e] of all sources s carry this step's epoch (acquire loads). Tiles
-//            are walked expert-major too, so the first tiles need what arrives first.
+//   source   its copies bound for destination d are one contiguous run of the sort (d's experts are
+//            consecutive), and copy j of that run goes to slot j of this source's region of d's receive
+//            buffer (what exceeds the capacity is cut). The slot space is cut into chunks of 8 rows and
+//            segments of 256 rows. Chunks are walked slot-major and round-robin over the destinations
+//            (chunk 0 of every destination, then chunk 1, ...), so every destination's slots fill from
+//            the front at about the same pace. A warp stores a chunk's rows straight into d's memory
+//            (plain stores through the peer mapping, i.e. over NVLink), fences, and counts the chunk;
+//            whoever completes a segment's last chunk publishes the step's epoch in d's flag
+//            [source][segment] with a system-scope release store.
+//   owner    before a gather warp of SDD reads the rows of a tile it waits, bounded, until the flags
+//            of the segments those rows lie in carry this step's epoch. The owner walks its row blocks
+//            in the order their last row's slot arrives (sb_ep_owner_layout writes that order), so the
+//            tensor cores follow the arrivals instead of waiting for the last row of the first expert.
 //
 // Nothing here waits for anything that itself waits: push warps never block, so two ranks' kernels
 // cannot wait for each other in a circle. Flags carry a monotonically growing epoch (the value of the
@@ -26,41 +31,33 @@
 namespace sb {
 
 constexpr int kPushChunkRows = 8;
+constexpr int kSegmentRows = 256;  // rows per arrival flag
+constexpr int kSegmentChunks = kSegmentRows / kPushChunkRows;
 
-// Upper bound of the chunks in a push plan: every (destination, expert) pair may end in a partial chunk, and an
-// empty pair still has one (it only signals).
-__host__ __device__ inline int64_t push_plan_max_chunks(int64_t n_copies, int32_t num_pairs) {
-  return (n_copies + kPushChunkRows - 1) / kPushChunkRows + num_pairs;
-}
-// Ints in a push plan: four arrays of num_pairs + 1, then one int4 per chunk (16-byte aligned).
-__host__ __device__ inline int64_t push_plan_ints(int64_t n_copies, int32_t num_pairs) {
-  const int64_t head = (4 * static_cast<int64_t>(num_pairs + 1) + 3) / 4 * 4;
-  return head + 4 * push_plan_max_chunks(n_copies, num_pairs);
+// Arrival flags (and the sender's chunk counters) per rank pair: one per segment of the capacity.
+__host__ __device__ inline int32_t dispatch_segments(int32_t capacity) {
+  return (capacity + kSegmentRows - 1) / kSegmentRows;
 }
 
 struct DispatchParams {
   // Source side.
-  const uint4* x;                // [T, D] this rank's token rows
-  const int32_t* sorted_token;   // [T*k] token of every sorted position (sort by global expert)
-  // Push plan, pair q = e * num_ranks + d. Four arrays of num_pairs + 1 ints back to back:
-  //   chunk_prefix | first_pos (sorted position of the run) | slot_start (first slot i at d) | kept (rows)
-  // then (at the next multiple of four ints) one int4 per chunk, in the order the chunks are pushed:
-  //   x = sorted position of its first row, y = its first row in the destination's buffer,
-  //   z = pair q, w = rows (low 8 bits) | chunks of the pair << 8.
-  const int32_t* plan;
-  uint4* const* peer_recv;       // [N] every rank's receive buffer [N * capacity, D]
-  uint32_t* const* peer_flags;   // [N] every rank's arrival flags [N * E_local]
-  uint32_t* done;                // [num_pairs] chunk counters of this rank, zero between kernels
+  const uint4* x;                 // [T, D] this rank's token rows
+  const int32_t* sorted_token;    // [T*k] token of every sorted position (sort by global expert)
+  const int32_t* expert_offsets;  // [N * E_local + 1] first sorted position of every global expert
+  uint4* const* peer_recv;        // [N] every rank's receive buffer [N * capacity, D]
+  uint32_t* const* peer_flags;    // [N] every rank's arrival flags [N * segments]
+  uint32_t* done;                 // [N * segments] chunk counters of this rank, zero between kernels
   // Owner side.
-  const uint32_t* my_flags;      // [N * E_local]
+  const uint32_t* my_flags;       // [N * segments], flag [s][g]: rows g*256 .. of source s are here
+  const int32_t* row_block_order; // [num_row_blocks] row blocks in the order to work on them, or null
   // Both: the word whose current value is this step's epoch (the exchange's barrier counter).
   const uint32_t* epoch_word;
   int32_t my_rank;
   int32_t num_ranks;
   int32_t experts_local;
   int32_t capacity;
-  int32_t vecs_per_row;          // D * 2 / 16
-  int32_t num_pairs;             // N * E_local
+  int32_t segments;               // dispatch_segments(capacity)
+  int32_t vecs_per_row;           // D * 2 / 16
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -68,6 +65,12 @@ __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acquire_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -93,57 +96,104 @@ __device__ __forceinline__ void copy_row_warp(const uint4* __restrict__ src, uin
   }
 }
 
-// One warp's share of the source side: chunks worker, worker + num_workers, ... of the push plan. A chunk is one
-// 16-byte record away (no search), its rows' tokens come with one coalesced load, and a row's loads are all in
-// flight before its stores: what is left per chunk is one memory latency per row and one system fence.
+// The same for TWO rows at once, for rows of whole groups of 256 vectors (2048 elements; the caller checks): sixteen
+// loads per lane in flight, no predicates. Inside a matmul kernel, whose TMA traffic keeps
+// the memory pipeline full, a load takes several microseconds to come back and a push warp is limited by the bytes
+// it has in flight (4 KB per warp gave 33 MB in about 95 us over the chip; 8 KB halves that).
+__device__ __forceinline__ void copy_two_rows_warp(const uint4* __restrict__ src0, const uint4* __restrict__ src1,
+                                                   uint4* __restrict__ dst0, uint4* __restrict__ dst1, int32_t vecs,
+                                                   int lane) {
+  for (int32_t v0 = lane; v0 < vecs; v0 += 32 * 8) {
+    uint4 a[8], b[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) a[q] = __ldg(src0 + v0 + 32 * q);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) b[q] = __ldg(src1 + v0 + 32 * q);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst0[v0 + 32 * q] = a[q];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) dst1[v0 + 32 * q] = b[q];
+  }
+}
+
+// One warp's share of the source side: chunks worker, worker + num_workers, ... of the slot-major, destination-
+// round-robin walk. Nothing is looked up but two sort offsets per chunk; a chunk's tokens come with one coalesced
+// load, and two rows' loads are in flight before their stores.
 __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker, int num_workers, int lane) {
-  const int32_t pairs = dp.num_pairs;
-  const int32_t total = __ldg(dp.plan + pairs);  // chunk_prefix[pairs]
-  const int4* table = reinterpret_cast<const int4*>(dp.plan + (4 * (pairs + 1) + 3) / 4 * 4);
+  const int32_t ranks = dp.num_ranks;
+  const int32_t total = dp.segments * kSegmentChunks * ranks;  // chunk positions, most of them past the rows
   const uint32_t epoch = *dp.epoch_word;
-  for (int32_t c = worker; c < total; c += num_workers) {
-    const int4 chunk = __ldg(table + c);
-    const int32_t q = chunk.z;
-    const int32_t rows = chunk.w & 0xff;  // 0: the one chunk of an empty pair, which only signals
-    const int32_t e = q / dp.num_ranks;
-    const int32_t d = q - e * dp.num_ranks;
-    if (rows > 0) {
-      const int32_t my_token = lane < rows ? __ldg(dp.sorted_token + chunk.x + lane) : 0;
-      uint4* dst = dp.peer_recv[d] + static_cast<int64_t>(chunk.y) * dp.vecs_per_row;
-      for (int32_t r = 0; r < rows; ++r) {
-        const int32_t token = __shfl_sync(0xffffffffu, my_token, r);
-        copy_row_warp(dp.x + static_cast<int64_t>(token) * dp.vecs_per_row, dst + static_cast<int64_t>(r) * dp.vecs_per_row,
-                      dp.vecs_per_row, lane);
-      }
-      __threadfence_system();  // this lane's rows are in the destination's memory before the count below
+  for (int32_t idx = worker; idx < total; idx += num_workers) {
+    const int32_t c = idx / ranks;  // chunk of the slot space: slots 8c .. 8c+7
+    // Rotated by the rank (sources start at different destinations) and by the chunk (a worker whose stride is a
+    // multiple of the rank count still visits every destination).
+    const int32_t d = (idx - c * ranks + dp.my_rank + c) % ranks;
+    const int32_t base = __ldg(dp.expert_offsets + d * dp.experts_local);
+    const int32_t kept = min(dp.capacity, __ldg(dp.expert_offsets + (d + 1) * dp.experts_local) - base);
+    const int32_t j0 = c * kPushChunkRows;
+    if (j0 >= kept) continue;
+    const int32_t rows = min(kPushChunkRows, kept - j0);
+    const int32_t my_token = lane < rows ? __ldg(dp.sorted_token + base + j0 + lane) : 0;
+    uint4* dst = dp.peer_recv[d] + (static_cast<int64_t>(dp.my_rank) * dp.capacity + j0) * dp.vecs_per_row;
+    int32_t r = 0;
+    for (; (dp.vecs_per_row & 255) == 0 && r + 1 < rows; r += 2) {
+      const int32_t token0 = __shfl_sync(0xffffffffu, my_token, r);
+      const int32_t token1 = __shfl_sync(0xffffffffu, my_token, r + 1);
+      copy_two_rows_warp(dp.x + static_cast<int64_t>(token0) * dp.vecs_per_row,
+                         dp.x + static_cast<int64_t>(token1) * dp.vecs_per_row,
+                         dst + static_cast<int64_t>(r) * dp.vecs_per_row,
+                         dst + static_cast<int64_t>(r + 1) * dp.vecs_per_row, dp.vecs_per_row, lane);
     }
+    for (; r < rows; ++r) {
+      const int32_t token = __shfl_sync(0xffffffffu, my_token, r);
+      copy_row_warp(dp.x + static_cast<int64_t>(token) * dp.vecs_per_row, dst + static_cast<int64_t>(r) * dp.vecs_per_row,
+                    dp.vecs_per_row, lane);
+    }
+    __threadfence_system();  // this lane's rows are in the destination's memory before the count below
     __syncwarp();
     if (lane == 0) {
-      const uint32_t chunks = static_cast<uint32_t>(chunk.w) >> 8;
-      if (atomicAdd(dp.done + q, 1u) + 1u == chunks) {
-        dp.done[q] = 0u;          // ready for the next step
+      const int32_t g = c / kSegmentChunks;
+      const int32_t seg_rows = min(kept, (g + 1) * kSegmentRows) - g * kSegmentRows;
+      const uint32_t chunks = static_cast<uint32_t>((seg_rows + kPushChunkRows - 1) / kPushChunkRows);
+      uint32_t* counter = dp.done + d * dp.segments + g;
+      if (atomicAdd(counter, 1u) + 1u == chunks) {
+        *counter = 0u;            // ready for the next step
         __threadfence_system();   // the other chunks' rows (fenced before their counts) before the flag
-        st_release_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.experts_local + e, epoch);
+        st_release_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.segments + g, epoch);
       }
     }
   }
 }
 
-// Owner side, whole warp: until every source has delivered its rows for local expert e in this step.
-// Lane s watches source s. Returns false when the wait ran out (1 s) or `*abort` was raised.
-__device__ __forceinline__ bool wait_expert_arrived(const DispatchParams& dp, int32_t e, uint32_t epoch, int lane,
-                                                    const volatile uint32_t* abort) {
-  const uint32_t* flag = dp.my_flags + (lane < dp.num_ranks ? lane : 0) * dp.experts_local + e;
+// Owner side, whole warp: until the eight receive slots this lane is about to gather (slot[j] < 0: a padding row,
+// nothing to wait for) lie in segments whose flag carries this step's epoch. The polls are relaxed loads (eight
+// acquire loads would each wait for the one before); one acquire fence after the last of them orders the gathers
+// behind the flags. Returns false when the wait ran out (1 s) or `*abort` was raised.
+__device__ __forceinline__ bool wait_rows_arrived(const DispatchParams& dp, const int32_t (&slot)[8], uint32_t epoch,
+                                                  const volatile uint32_t* abort) {
+  const uint32_t* flag[8];
+  uint32_t pending = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int32_t source = slot[j] >= 0 ? slot[j] / dp.capacity : 0;
+    const int32_t within = slot[j] >= 0 ? slot[j] - source * dp.capacity : 0;
+    flag[j] = dp.my_flags + source * dp.segments + within / kSegmentRows;
+    if (slot[j] >= 0) pending |= 1u << j;
+  }
   const uint64_t start = dispatch_timer_ns();
   for (uint32_t poll = 0;; ++poll) {
-    const bool here = lane >= dp.num_ranks || static_cast<int32_t>(ld_acquire_sys_u32(flag) - epoch) >= 0;
-    if (__all_sync(0xffffffffu, here)) return true;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if ((pending >> j & 1u) && static_cast<int32_t>(ld_relaxed_sys_u32(flag[j]) - epoch) >= 0) pending &= ~(1u << j);
+    if (__all_sync(0xffffffffu, pending == 0u)) break;
     if ((poll & 31u) == 31u) {
       const bool stop = *abort != 0u || dispatch_timer_ns() - start > 1000ull * 1000ull * 1000ull;
       if (__any_sync(0xffffffffu, stop)) return false;
     }
     __nanosleep(100);
   }
+  fence_acquire_sys();
+  return true;
 }
 
 }  // namespace sb

@@ -536,13 +536,21 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
 // exactly those arrays, bit for bit, from N * E_local counts instead of N * capacity ids, in one
 // launch. Every block recomputes the small tables in shared memory and takes a share of the rows.
 // Needs N * E_local <= 1024 (one thread per (source, expert) pair).
+//
+// row_block_order (optional): the row blocks sorted by when their rows are complete if every source fills
+// its slots from the front at the same pace, i.e. by the largest slot index i among the block's rows (ties
+// in layout order, blocks without rows last). Block 0 computes the keys into shared memory and ranks them
+// by counting (at most 4096 row blocks: a few hundred in practice).
 constexpr int kOwnerThreads = 1024;
+constexpr int kMaxOrderedRowBlocks = 4096;
 
 __global__ void __launch_bounds__(kOwnerThreads, 1)
 ep_owner_layout_kernel(const int32_t* __restrict__ recv_counts, int32_t num_ranks, int32_t experts_local,
                        int32_t capacity, int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks,
                        int32_t* __restrict__ tokens_per_expert, int32_t* __restrict__ padded_offsets,
-                       int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ error) {
+                       int32_t* __restrict__ copy_row, LayoutOut layout, int32_t* __restrict__ row_block_order,
+                       int32_t* __restrict__ error) {
+  __shared__ int32_t arrival_key[kMaxOrderedRowBlocks];
   __shared__ int32_t kept[kMaxExperts];        // [s][e] copies of e from s that fit the capacity
   __shared__ int32_t slot_start[kMaxExperts];  // [s][e] first slot index i of that run
   __shared__ int32_t row_start[kMaxExperts];   // [s][e] first row of that run in the layout
@@ -617,6 +625,38 @@ ep_owner_layout_kernel(const int32_t* __restrict__ recv_counts, int32_t num_rank
   // Padding rows, rows past the end and the block-sparse arrays.
   fill_layout(offsets, counts, experts_local, block_size, ffn_blocks, max_row_blocks, layout, warp_index, warp_count,
               lane);
+  if (row_block_order == nullptr || blockIdx.x != 0) return;
+  for (int32_t rb = tid; rb < max_row_blocks; rb += kOwnerThreads) {
+    const int32_t first = rb * block_size;
+    int32_t key = INT32_MAX;
+    if (first < offsets[experts_local]) {
+      int32_t lo = 0, hi = experts_local;  // the expert e with offsets[e] <= first < offsets[e + 1]
+      while (hi - lo > 1) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (offsets[mid] <= first) lo = mid; else hi = mid;
+      }
+      const int32_t e = lo;
+      const int32_t end = min(first + block_size, offsets[e] + counts[e]);
+      key = -1;
+      for (int32_t src = 0; src < num_ranks; ++src) {
+        const int32_t run = row_start[src * experts_local + e];
+        const int32_t from = max(first, run);
+        const int32_t to = min(end, run + kept[src * experts_local + e]);
+        if (from < to) key = max(key, slot_start[src * experts_local + e] + (to - 1 - run));
+      }
+    }
+    arrival_key[rb] = key;
+  }
+  __syncthreads();
+  for (int32_t rb = tid; rb < max_row_blocks; rb += kOwnerThreads) {
+    const int32_t key = arrival_key[rb];
+    int32_t rank = 0;
+    for (int32_t other = 0; other < max_row_blocks; ++other) {
+      const int32_t k2 = arrival_key[other];
+      rank += (k2 < key || (k2 == key && other < rb)) ? 1 : 0;
+    }
+    row_block_order[rank] = rb;
+  }
 }
 
 size_t cluster_smem_bytes(int32_t num_experts) {
@@ -887,8 +927,12 @@ int sb_route_from_logits(const void* logits, int logits_dtype, int64_t num_token
 int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,
                        int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
                        int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,
-                       int32_t* row_offsets, int32_t* col_indices, int32_t* error, sb_stream_t stream) {
+                       int32_t* row_offsets, int32_t* col_indices, int32_t* row_block_order, int32_t* error,
+                       sb_stream_t stream) {
   sb::clear_error();
+  if (row_block_order != nullptr && max_row_blocks > sb::kMaxOrderedRowBlocks)
+    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: the arrival order is built for at most %d row blocks, not %d",
+                    sb::kMaxOrderedRowBlocks, max_row_blocks);
   if (num_ranks <= 0 || experts_local <= 0 || static_cast<int64_t>(num_ranks) * experts_local > sb::kMaxExperts)
     return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: need 0 < ranks * local experts <= %d", sb::kMaxExperts);
   if (capacity <= 0 || ffn_blocks <= 0) return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: capacity and ffn_blocks must be positive");
@@ -911,7 +955,7 @@ int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t ex
   const sb::LayoutOut layout{row_token, row_block_expert, row_offsets, col_indices};
   sb::ep_owner_layout_kernel<<<static_cast<unsigned>(blocks), sb::kOwnerThreads, 0, sb::as_stream(stream)>>>(
       recv_counts, num_ranks, experts_local, capacity, ffn_blocks, block_size, static_cast<int32_t>(max_row_blocks),
-      tokens_per_expert, padded_offsets, copy_row, layout, error);
+      tokens_per_expert, padded_offsets, copy_row, layout, row_block_order, error);
   return sb::check_launch("ep_owner_layout");
 }
 

@@ -91,13 +91,14 @@ extern "C" int sb_sdd(const void* x, const void* w1, const int32_t* row_token, c
 extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const int32_t* row_slot,
                                   const int32_t* row_block_expert, const int32_t* row_offsets, void* h_blocks,
                                   int32_t d_model, int32_t ffn_dim, int32_t num_row_blocks, const void* x,
-                                  const int32_t* sorted_token, const int32_t* plan, void* const* peer_recv,
+                                  const int32_t* sorted_token, const int32_t* expert_offsets,
+                                  const int32_t* row_block_order, void* const* peer_recv,
                                   uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
                                   const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks,
                                   int32_t experts_local, int32_t capacity, int32_t* dev_status, sb_stream_t stream) {
   using namespace sb;
   clear_error();
-  if (!x || !sorted_token || !plan || !peer_recv || !peer_flags || !my_flags || !done || !epoch_word)
+  if (!x || !sorted_token || !expert_offsets || !peer_recv || !peer_flags || !my_flags || !done || !epoch_word)
     return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: NULL buffer");
   if (num_ranks <= 0 || num_ranks > 32 || my_rank < 0 || my_rank >= num_ranks || experts_local <= 0 || capacity <= 0)
     return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: need 0 <= rank < ranks <= 32, local experts > 0, capacity > 0");
@@ -105,18 +106,19 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
   DispatchParams dp{};
   dp.x = static_cast<const uint4*>(x);
   dp.sorted_token = sorted_token;
-  dp.plan = plan;
+  dp.expert_offsets = expert_offsets;
   dp.peer_recv = reinterpret_cast<uint4* const*>(peer_recv);
   dp.peer_flags = peer_flags;
   dp.done = done;
   dp.my_flags = my_flags;
+  dp.row_block_order = row_block_order;
   dp.epoch_word = epoch_word;
   dp.my_rank = my_rank;
   dp.num_ranks = num_ranks;
   dp.experts_local = experts_local;
   dp.capacity = capacity;
+  dp.segments = dispatch_segments(capacity);
   dp.vecs_per_row = d_model / 8;
-  dp.num_pairs = num_ranks * experts_local;
   return sdd_launch(recv_rows, w1, row_slot, row_block_expert, row_offsets, h_blocks,
                     static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, nullptr,
                     &dp, dev_status, stream);

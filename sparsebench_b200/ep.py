@@ -18,9 +18,10 @@ slices of w1/w2 never move) and T local tokens. One step on a rank:
 
 With the peer exchange both legs ride inside the owner's matmul kernels. Dispatch: only the
 per-expert COUNTS are exchanged up front (they are all the owner's layout needs); the rows are
-pushed by extra warps of the SDD kernel itself, expert by expert, and every SDD tile waits, bounded,
-for the arrival flags of its expert, so the rows travel while the tensor cores already work on what
-has arrived. Return: the DSD epilogue stores each result row into its source rank's buffer (no y, no
+pushed by extra warps of the SDD kernel itself, every destination's slots from the front, and every SDD
+tile waits, bounded, for the arrival flags of the 256-row segments its rows lie in; the owner walks its
+row blocks in the order they become complete, so the rows travel while the tensor cores already work
+on what has arrived. Return: the DSD epilogue stores each result row into its source rank's buffer (no y, no
 second kernel). Two device-side barriers remain per step: a light one after the counts, and the
 one before the combine.
 
@@ -114,27 +115,23 @@ class CudaOps:
 
         _C.ep_barrier(peer_pads, my_pad, epoch, my_rank, status)
 
-    def dispatch_plan(self, expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts, n_copies):
-        """The source's push plan; also stores this rank's counts into every owner's table."""
-        from sparsebench_b200 import _C
-
-        return _C.ep_dispatch_plan(expert_offsets, num_ranks, experts_per_rank, capacity, my_rank, peer_counts, n_copies)
-
-    def owner_layout(self, recv_counts: torch.Tensor, capacity: int, ffn_dim: int):
-        """The owner's layout over its receive slots from the exchanged counts alone."""
+    def owner_layout(self, recv_counts: torch.Tensor, capacity: int, ffn_dim: int, arrival_order: bool = False):
+        """The owner's layout over its receive slots from the exchanged counts alone; with arrival_order, also the
+        order in which its row blocks become complete (a second return value)."""
         from sparsebench_b200 import _C
         from sparsebench_b200.routing import DeviceTopology
 
-        out = _C.ep_owner_layout(recv_counts, capacity, ffn_dim, BLOCK_SIZE)
-        return DeviceTopology(BLOCK_SIZE, recv_counts.shape[1], ffn_dim // BLOCK_SIZE, *out)
+        out = _C.ep_owner_layout(recv_counts, capacity, ffn_dim, BLOCK_SIZE, arrival_order)
+        topo = DeviceTopology(BLOCK_SIZE, recv_counts.shape[1], ffn_dim // BLOCK_SIZE, *out[:8])
+        return (topo, out[8]) if arrival_order else topo
 
-    def sdd_dispatch(self, peer, w1, topo, x, sorted_token, plan, my_rank, capacity):
+    def sdd_dispatch(self, peer, w1, topo, order, x, sorted_token, expert_offsets, my_rank, capacity):
         """SDD over rows that are still arriving, with this rank's own pushes in the same kernel."""
         from sparsebench_b200 import _C
 
         return _C.ep_sdd_dispatch(peer.recv, w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
-                                  topo.col_indices.numel(), x, sorted_token, plan, peer.peer_recv, peer.peer_flags,
-                                  peer.flags, peer.done, peer.epoch, my_rank, capacity)
+                                  topo.col_indices.numel(), x, sorted_token, expert_offsets, order, peer.peer_recv,
+                                  peer.peer_flags, peer.flags, peer.done, peer.epoch, my_rank, capacity)
 
 
 class PeerExchange:
@@ -142,7 +139,8 @@ class PeerExchange:
     handles exchanged once at set-up), so that rows are stored straight into their owner's memory
     over NVLink and only real rows travel. Holds, per rank: recv [N*C, D] (dispatched rows, block s
     from rank s), ret [N*C, D] (results coming back, block d from rank d), counts [N, E/N], a pad
-    of N words for the device-side barrier and N * E/N arrival flags (one per source and local expert)."""
+    of N words for the device-side barrier and N * ceil(C / 256) arrival flags (one per source and 256-row
+    segment of its block of recv)."""
 
     def __init__(self, group: dist.ProcessGroup, device: torch.device, capacity: int, d_model: int,
                  experts_local: int, dtype: torch.dtype = torch.bfloat16) -> None:
@@ -158,7 +156,8 @@ class PeerExchange:
         rows_bytes = aligned(world * capacity * d_model * elem)
         counts_bytes = aligned(world * experts_local * 4)
         pad_bytes = aligned(world * 4)
-        flags_bytes = aligned(world * experts_local * 4)
+        segments = (capacity + 255) // 256  # sb_ep_dispatch_segments
+        flags_bytes = aligned(world * segments * 4)
         offsets = [0, rows_bytes, 2 * rows_bytes, 2 * rows_bytes + counts_bytes, 2 * rows_bytes + counts_bytes + pad_bytes]
         total = offsets[4] + flags_bytes
         self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
@@ -174,7 +173,7 @@ class PeerExchange:
         self.ret = view(offsets[1], world * capacity * d_model * elem, dtype).view(world * capacity, d_model)
         self.counts = view(offsets[2], world * experts_local * 4, torch.int32).view(world, experts_local)
         self.pad = view(offsets[3], world * 4, torch.int32)
-        self.flags = view(offsets[4], world * experts_local * 4, torch.int32)
+        self.flags = view(offsets[4], world * segments * 4, torch.int32)
         bases = [int(p) for p in self.handle.buffer_ptrs]
 
         def table(off: int) -> torch.Tensor:
@@ -184,7 +183,7 @@ class PeerExchange:
         self.peer_counts, self.peer_pads = table(offsets[2]), table(offsets[3])
         self.peer_flags = table(offsets[4])
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
-        self.done = torch.zeros(world * experts_local, dtype=torch.int32, device=device)  # push chunk counters
+        self.done = torch.zeros(world * segments, dtype=torch.int32, device=device)  # push chunk counters
 
 
 @dataclass
@@ -401,13 +400,13 @@ class ExpertParallelMoE:
         ops = self.ops
         _, offsets, sorted_token, _ = source_sort
         x = x.contiguous()
-        plan = ops.dispatch_plan(offsets, self.world, self.experts_local, capacity, self.rank, peer.peer_counts,
-                                 sorted_token.numel())
+        counts = source_sort[0]
+        ops.push_counts(counts, peer.peer_counts, self.rank, self.experts_local)
         ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)  # counts only: nothing heavy to wait for
         mark("dispatch all-to-all")
-        topo = ops.owner_layout(peer.counts, capacity, self.ffn_dim)
+        topo, order = ops.owner_layout(peer.counts, capacity, self.ffn_dim, arrival_order=True)
         mark("routing")
-        h = ops.sdd_dispatch(peer, self.w1, topo, x, sorted_token, plan, self.rank, capacity)
+        h = ops.sdd_dispatch(peer, self.w1, topo, order, x, sorted_token, offsets, self.rank, capacity)
         if after_dispatch is not None:
             after_dispatch()
         mark("SDD + GELU (fused)")

@@ -111,26 +111,25 @@ class CpuOps:
         return (rows.float() * expert_weight.float()[..., None]).sum(dim=1)
 
 
-def dispatch_plan(offsets: np.ndarray, num_ranks: int, experts_per_rank: int, capacity: int, my_rank: int,
-                  chunk_rows: int = 8):
-    """numpy restatement of sb_ep_dispatch_plan: (chunk_prefix [pairs+1], first_pos, slot_start, kept [pairs],
-    chunk records [total, 4]) with pair q = e * N + d, the order the rows are pushed in."""
-    pairs = num_ranks * experts_per_rank
-    prefix = np.zeros(pairs + 1, dtype=np.int64)
-    first_pos, slot_start, kept = (np.zeros(pairs, dtype=np.int64) for _ in range(3))
-    records = []
-    for q in range(pairs):
-        e, d = divmod(q, num_ranks)
-        g = d * experts_per_rank + e
-        first = int(offsets[g])
-        count = int(offsets[g + 1]) - first
-        in_run = first - int(offsets[d * experts_per_rank])
-        begin = min(capacity, in_run)
-        rows = min(capacity, in_run + count) - begin
-        chunks = max(1, -(-rows // chunk_rows))
-        first_pos[q], slot_start[q], kept[q] = first, begin, rows
-        prefix[q + 1] = prefix[q] + chunks
-        for i in range(chunks):
-            n = max(0, min(chunk_rows, rows - i * chunk_rows))
-            records.append((first + i * chunk_rows, my_rank * capacity + begin + i * chunk_rows, q, n | (chunks << 8)))
-    return prefix, first_pos, slot_start, kept, np.array(records, dtype=np.int64).reshape(-1, 4)
+def kept_rows(offsets: np.ndarray, num_ranks: int, experts_per_rank: int, capacity: int) -> np.ndarray:
+    """Rows a source pushes to every destination d: its copies for d's experts, cut at the capacity."""
+    starts = offsets[:: experts_per_rank][: num_ranks + 1].astype(np.int64)
+    return np.minimum(capacity, starts[1:] - starts[:-1])
+
+
+def segment_flags(offsets: np.ndarray, num_ranks: int, experts_per_rank: int, capacity: int,
+                  segment_rows: int = 256) -> np.ndarray:
+    """numpy restatement of which arrival flags a source raises (sb_ep_push_rows_flagged): [d][g] = 1 when segment g
+    (slots g * 256 ...) of its block at destination d holds at least one row."""
+    segments = -(-capacity // segment_rows)
+    kept = kept_rows(offsets, num_ranks, experts_per_rank, capacity)
+    return (kept[:, None] > np.arange(segments)[None, :] * segment_rows).astype(np.int32)
+
+
+def arrival_order(row_token: np.ndarray, capacity: int, block_size: int) -> np.ndarray:
+    """numpy restatement of sb_ep_owner_layout's row_block_order: row blocks sorted by the largest slot index
+    (within its source's block of `capacity` slots) among their rows; ties in layout order, blocks without rows last."""
+    rows = np.asarray(row_token, dtype=np.int64).reshape(-1, block_size)
+    within = np.where(rows >= 0, rows % capacity, -1)
+    keys = np.where((rows >= 0).any(axis=1), within.max(axis=1), np.iinfo(np.int32).max)
+    return np.argsort(keys, kind="stable").astype(np.int32)

@@ -217,28 +217,21 @@ def test_owner_layout_from_counts_equals_routing_of_the_slots(ranks: int, expert
                              experts_local, ffn_dim, 128)
     for name, a in zip(names, got):
         assert np.array_equal(a.cpu().numpy(), getattr(oracle, name)), name
+    # The arrival order: same eight arrays, plus the row blocks sorted by their last-arriving slot.
+    with_order = _C.ep_owner_layout(recv_counts.cuda(), capacity, ffn_dim, arrival_order=True)
+    for name, a, b in zip(names, with_order, got):
+        assert torch.equal(a, b), name
+    want_order = ep_cpu_ops.arrival_order(oracle.row_token, capacity, 128)
+    assert np.array_equal(with_order[8].cpu().numpy(), want_order)
+    assert sorted(want_order.tolist()) == list(range(len(want_order)))
 
 
-@pytest.mark.parametrize(("num_tokens", "num_experts", "ranks", "capacity"),
-                         [(300, 8, 2, 600), (300, 8, 4, 40), (4096, 128, 8, 8192), (1, 4, 2, 8)])
-def test_dispatch_plan_matches_the_restatement(num_tokens: int, num_experts: int, ranks: int, capacity: int) -> None:
+def _C_segments(capacity: int) -> int:
     from sparsebench_b200 import _C
 
-    idx = routing_case("zipf", num_tokens, num_experts, seed=4)
-    _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx.cuda(), num_experts)
-    per_rank = num_experts // ranks
-    pairs = num_experts
-    for my_rank in (0, ranks - 1):
-        plan = _C.ep_dispatch_plan(offsets, ranks, per_rank, capacity, my_rank, None, sorted_token.numel()).cpu().numpy()
-        prefix, first_pos, slot_start, kept, records = ep_cpu_ops.dispatch_plan(offsets.cpu().numpy(), ranks, per_rank,
-                                                                                capacity, my_rank)
-        assert np.array_equal(plan[: pairs + 1], prefix)
-        assert np.array_equal(plan[pairs + 1: 2 * pairs + 1], first_pos)
-        assert np.array_equal(plan[2 * (pairs + 1): 2 * (pairs + 1) + pairs], slot_start)
-        assert np.array_equal(plan[3 * (pairs + 1): 3 * (pairs + 1) + pairs], kept)
-        head = (4 * (pairs + 1) + 3) // 4 * 4
-        assert np.array_equal(plan[head: head + 4 * len(records)].reshape(-1, 4), records)
-        assert len(records) <= (sorted_token.numel() + 7) // 8 + pairs
+    segments = _C.ep_dispatch_segments(capacity)
+    assert segments == (capacity + 255) // 256
+    return segments
 
 
 class LocalExchange:
@@ -247,13 +240,14 @@ class LocalExchange:
 
     def __init__(self, ranks: int, capacity: int, d_model: int, experts_local: int) -> None:
         dev = "cuda"
+        self.segments = _C_segments(capacity)
         self.recv = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=dev)
         self.ret = torch.zeros(ranks, ranks * capacity, d_model, dtype=torch.bfloat16, device=dev)
         self.counts = torch.zeros(ranks, ranks, experts_local, dtype=torch.int32, device=dev)
         self.pad = torch.zeros(ranks, ranks, dtype=torch.int32, device=dev)
-        self.flags = torch.zeros(ranks, ranks * experts_local, dtype=torch.int32, device=dev)
+        self.flags = torch.zeros(ranks, ranks * self.segments, dtype=torch.int32, device=dev)
         self.epoch = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(ranks)]
-        self.done = [torch.zeros(ranks * experts_local, dtype=torch.int32, device=dev) for _ in range(ranks)]
+        self.done = [torch.zeros(ranks * self.segments, dtype=torch.int32, device=dev) for _ in range(ranks)]
 
         def table(t: torch.Tensor) -> torch.Tensor:
             return torch.tensor([t[r].data_ptr() for r in range(ranks)], dtype=torch.int64, device=dev)
@@ -271,14 +265,16 @@ class LocalExchange:
             peer_counts=self.peer_counts, peer_pads=self.peer_pads, peer_flags=self.peer_flags)
 
 
-@pytest.mark.parametrize(("ranks", "capacity"), [(2, 600), (4, 40)])
-def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_every_flag(ranks: int, capacity: int) -> None:
+@pytest.mark.parametrize(("ranks", "capacity", "num_tokens"), [(2, 600, 300), (4, 40, 300), (2, 1024, 1500)])
+def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_the_segment_flags(ranks: int, capacity: int,
+                                                                                     num_tokens: int) -> None:
     from sparsebench_b200 import _C
 
-    num_tokens, num_experts, d_model = 300, 16, 256
+    num_experts, d_model = 16, 256
     experts_local = num_experts // ranks
     g = torch.Generator().manual_seed(5)
     old, new = LocalExchange(ranks, capacity, d_model, experts_local), LocalExchange(ranks, capacity, d_model, experts_local)
+    want_flags = torch.zeros(ranks, ranks * new.segments, dtype=torch.int32)
     for rank in range(ranks):  # one virtual rank at a time
         x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
         idx = routing_case("zipf", num_tokens, num_experts, seed=rank).cuda()
@@ -289,18 +285,20 @@ def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_every_flag(ra
         _C.ep_push_rows(x, send_index, old.peer_recv, rank, capacity)
         view = new.of(rank)
         view.epoch.fill_(7)
-        plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, new.peer_counts, sorted_token.numel())
-        _C.ep_push_rows_flagged(x, sorted_token, plan, new.peer_recv, new.peer_flags, view.done, view.epoch, rank,
+        _C.ep_push_counts(counts, new.peer_counts, rank, experts_local)
+        _C.ep_push_rows_flagged(x, sorted_token, offsets, new.peer_recv, new.peer_flags, view.done, view.epoch, rank,
                                 experts_local, capacity)
         torch.cuda.synchronize()
         assert int(view.done.abs().sum().item()) == 0, "chunk counters must be left at zero"
-        pairs = ranks * experts_local
-        chunk_prefix, kept = plan[: pairs + 1].cpu(), plan[3 * (pairs + 1): 3 * (pairs + 1) + pairs].cpu()
-        assert int(kept.sum().item()) == int((send_index >= 0).sum().item())
-        assert torch.equal(chunk_prefix[1:] - chunk_prefix[:-1], torch.clamp((kept + 7) // 8, min=1).to(torch.int32))
+        raised = ep_cpu_ops.segment_flags(offsets.cpu().numpy(), ranks, experts_local, capacity)  # [d][g]
+        assert int(ep_cpu_ops.kept_rows(offsets.cpu().numpy(), ranks, experts_local, capacity).sum()) == \
+            int((send_index >= 0).sum().item())
+        for d in range(ranks):
+            want_flags[d, rank * new.segments: (rank + 1) * new.segments] = torch.from_numpy(raised[d]) * 7
     assert torch.equal(new.recv, old.recv)
     assert torch.equal(new.counts, old.counts)
-    assert bool((new.flags == 7).all()), "every (source, expert) flag at every owner carries the epoch"
+    assert torch.equal(new.flags.cpu(), want_flags), "exactly the segments that hold rows carry the epoch"
+    assert bool((want_flags == 7).any()) and (capacity < 256 or bool((want_flags == 0).any()))
 
 
 @pytest.mark.parametrize("case", ["zipf", "random", "empty_middle"])
@@ -344,23 +342,24 @@ def test_two_virtual_ranks_overlapped_dispatch_matches_oracle() -> None:
     ex = LocalExchange(ranks, capacity, d_model, experts_local)
     xs = [torch.randn(num_tokens, d_model, generator=g).bfloat16() for _ in range(ranks)]
     idxs = [routing_case("random", num_tokens, num_experts, seed=10 + r) for r in range(ranks)]
-    plans, sorts = [], []
+    starts, sorts = [], []
     for rank in range(ranks):
         ex.epoch[rank].fill_(3)
-        _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idxs[rank].cuda(), num_experts)
-        plans.append(_C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, rank, ex.peer_counts, sorted_token.numel()))
+        counts, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idxs[rank].cuda(), num_experts)
+        _C.ep_push_counts(counts, ex.peer_counts, rank, experts_local)
+        starts.append(offsets)
         sorts.append(sorted_token)
     x_dev = [x.cuda() for x in xs]
     view1 = ex.of(1)
-    _C.ep_push_rows_flagged(x_dev[1], sorts[1], plans[1], ex.peer_recv, ex.peer_flags, view1.done, view1.epoch, 1,
+    _C.ep_push_rows_flagged(x_dev[1], sorts[1], starts[1], ex.peer_recv, ex.peer_flags, view1.done, view1.epoch, 1,
                             experts_local, capacity)
     torch.cuda.synchronize()
     view0 = ex.of(0)
-    out = _C.ep_owner_layout(view0.counts, capacity, ffn_dim)
+    *out, order = _C.ep_owner_layout(view0.counts, capacity, ffn_dim, arrival_order=True)
     topo = DeviceTopology(128, experts_local, ffn_dim // 128, *out)
     h = _C.ep_sdd_dispatch(view0.recv, w1[:experts_local].cuda(), topo.row_token, topo.row_block_expert, topo.row_offsets,
-                           topo.col_indices.numel(), x_dev[0], sorts[0], plans[0], ex.peer_recv, ex.peer_flags, view0.flags,
-                           view0.done, view0.epoch, 0, capacity)
+                           topo.col_indices.numel(), x_dev[0], sorts[0], starts[0], order, ex.peer_recv, ex.peer_flags,
+                           view0.flags, view0.done, view0.epoch, 0, capacity)
     torch.cuda.synchronize()
     # Oracle: rank 0 owns experts [0, experts_local); its rows are the global batch's rows of those experts.
     x_all, idx_all = torch.cat(xs), torch.cat(idxs)
@@ -393,23 +392,24 @@ def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers
     x = torch.randn(num_tokens, d_model, generator=g).bfloat16().cuda()
     w1 = torch.randn(experts_local, d_model, ffn_dim, generator=g).bfloat16().cuda()
     idx = routing_case("random", num_tokens, num_experts, seed=0).cuda()
-    _, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx, num_experts)
+    counts, offsets, sorted_token, _, _ = _C.sort_copies_cuda(idx, num_experts)
     view = ex.of(0)
     view.epoch.fill_(1)
-    plan = _C.ep_dispatch_plan(offsets, ranks, experts_local, capacity, 0, ex.peer_counts, sorted_token.numel())
+    _C.ep_push_counts(counts, ex.peer_counts, 0, experts_local)
     view.counts[1] = view.counts[0]  # pretend rank 1 announced rows that never come
     topo = DeviceTopology(128, experts_local, ffn_dim // 128, *_C.ep_owner_layout(view.counts, capacity, ffn_dim))
     status = _C.device_status(torch.device("cuda", torch.cuda.current_device()))
     torch.cuda.synchronize()
     started = time.perf_counter()
     _C.ep_sdd_dispatch(view.recv, w1, topo.row_token, topo.row_block_expert, topo.row_offsets, topo.col_indices.numel(),
-                       x, sorted_token, plan, ex.peer_recv, ex.peer_flags, view.flags, view.done, view.epoch, 0, capacity)
+                       x, sorted_token, offsets, None, ex.peer_recv, ex.peer_flags, view.flags, view.done, view.epoch, 0,
+                       capacity)
     torch.cuda.synchronize()
     waited = time.perf_counter() - started
     word = int(status.item())
     status.zero_()
     assert word & 8, f"SB_DEV_TIMEOUT_DISPATCH expected in the status word, got {word}"
     assert 0.5 < waited < 20.0
-    assert bool((ex.flags[0, :experts_local] == 1).all()) and bool((ex.flags[0, experts_local:] == 0).all())
+    assert ex.flags[0].tolist() == [1, 0], "rank 0's own segment arrived, rank 1's never did"
     # Still healthy: the plain kernel runs.
     assert int(_C.arch_probe(4)[0].item()) == 1000
