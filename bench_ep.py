@@ -30,10 +30,20 @@ from sparsebench_b200.workloads import CONFIGS, _weights, make_layer  # noqa: E4
 NVLINK_GBS_PER_DIRECTION = 770.0  # measured peer-to-peer copy bandwidth of one B200 over NVLink 5; 900 nominal
 PARITY_ROWS_PER_RANK = 32
 
-# Micro-batches per step by rank count, where measured to pay; elsewhere the step runs whole. With the dispatch
-# overlapped inside the owner's SDD kernel the exchange already hides behind the matmuls, and every part would
-# stream the owner's expert weights again.
-DEFAULT_MICRO_BATCHES: dict[int, int] = {}
+# The form of the peer-exchange step per rank count, as measured on this machine: (dispatch overlapped inside the
+# owner's SDD kernel, micro-batches pipelined over streams). Rank counts that are not listed run the plainest form.
+DEFAULT_EP_FORM: dict[int, tuple[bool, int]] = {2: (False, 1), 4: (False, 1), 8: (False, 2)}
+DEFAULT_MICRO_BATCHES: dict[int, int] = {n: form[1] for n, form in DEFAULT_EP_FORM.items()}
+
+
+def overlapped_dispatch_wanted(args, world: int) -> bool:
+    """--ep-dispatch overlapped / separate, the older --ep-unfused-dispatch, else the table above."""
+    choice = getattr(args, "ep_dispatch", "auto")
+    if getattr(args, "ep_unfused_dispatch", False) or choice == "separate":
+        return False
+    if choice == "overlapped":
+        return True
+    return DEFAULT_EP_FORM.get(world, (False, 1))[0]
 
 
 
@@ -338,16 +348,28 @@ def run_owner_profile(args) -> None:
         torch.cuda.synchronize()
         *layout, order = _C.ep_owner_layout(view.counts, capacity, cfg.ffn_dim, arrival_order=True)
         topo = DeviceTopology(128, experts_local, cfg.ffn_dim // 128, *layout)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        torch.cuda._sleep(2_000_000)  # about a millisecond of GPU time: the launches below queue up behind it
+        marks[0].record()
         h = _C.ep_sdd_dispatch(view.recv, mine.w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
-                               topo.col_indices.numel(), xs[0], sorts[0], starts[0], order, ex.peer_recv, ex.peer_flags,
+                               topo.col_indices.numel(), xs[0], sorts[0], starts[0],
+                               order, ex.peer_recv, ex.peer_flags,
                                view.flags, view.done, view.epoch, 0, capacity)
+        marks[1].record()
         _C.ep_dsd_push(h, w2_cat, topo.row_offsets, topo.col_indices, topo.row_token, ex.peer_ret, 0, capacity)
+        marks[2].record()
+        _C.sdd_cuda(view.recv, mine.w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
+                    topo.col_indices.numel(), True, True, topo.padded_offsets)
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[3].record()
         torch.cuda.synchronize()
+        kernel_ms = {"sdd_with_pushes": marks[0].elapsed_time(marks[1]), "dsd_with_return": marks[1].elapsed_time(marks[2]),
+                     "plain_sdd_same_layout": marks[2].elapsed_time(marks[3])}
     status = int(_C.device_status(device).item())
     rows = int(topo.padded_offsets[-1].item())
     print(json.dumps({"profile": "expert-parallel owner, rank 0 of 8 on one GPU", "steps": 3, "padded_rows": rows,
                       "received_rows": int(view.counts.sum().item()), "capacity_rows_per_pair": capacity,
-                      "device_status": status}))
+                      "last_step_kernel_ms": kernel_ms, "device_status": status}))
     if status != 0:
         raise SystemExit("a bounded device-side wait expired")
 
@@ -410,7 +432,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         try:
             moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
                                     fuse_return=not getattr(args, "ep_unfused_return", False),
-                                    fuse_dispatch=not getattr(args, "ep_unfused_dispatch", False),
+                                    fuse_dispatch=overlapped_dispatch_wanted(args, world),
                                     micro_batches=micro_batches)
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line

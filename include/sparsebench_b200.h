@@ -352,10 +352,12 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * counts alone (recv_counts [N][experts_local]), in one launch: the arrays sb_route writes when it is
  * handed sb_ep_slot_experts' output as a k = 1 problem, bit for bit (row_token holds receive-slot
  * indices; error is always 0). N * experts_local <= 1024. max_row_blocks as sb_route_sizes gives for
- * N * capacity copies. row_block_order (NULL: not wanted; needs max_row_blocks <= 4096): the row blocks
- * sorted by the largest slot index (within its source's region) among their rows, ties in layout order,
- * row blocks without rows last: the order in which their rows become complete when every source fills
- * its slots from the front.
+ * N * capacity copies. row_block_order (NULL: not wanted; needs max_row_blocks <= 4096, N <= 31, block_size <= 256):
+ * the owner's schedule, sb_ep_dispatch_schedule_ints(max_row_blocks) ints. First max_row_blocks entries: the row
+ * blocks sorted by the largest slot index (within its source's region) among their rows, ties in layout order,
+ * row blocks without rows last: the order in which their rows become complete when every source fills its slots
+ * from the front. Then 64 ints per row block: how many arrival flags its rows depend on, followed by their
+ * indices source * segments + segment.
  *
  * sb_ep_push_rows_flagged: the source side as a kernel of its own. When the last chunk of segment g of
  * destination d is in, peer_flags[d][my_rank * segments + g] is set to the current value of *epoch_word
@@ -366,13 +368,14 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * sb_ep_sdd_dispatch: sb_sdd over the receive buffer with both sides of that protocol inside the
  * matmul kernel: six extra warps per thread block do this rank's pushes (as a source), and the
  * gather warps wait, per tile, until the segments that hold the tile's rows have arrived (as an owner:
- * my_flags, this rank's flag array [N * segments]). Tiles are walked in row_block_order (NULL: layout
- * order). The wait is bounded (1 s): on expiry SB_DEV_TIMEOUT_DISPATCH is
+ * my_flags, this rank's flag array [N * segments]). row_block_order: sb_ep_owner_layout's schedule; tiles
+ * are walked in its order and wait for the flags of its lists (NULL: layout order, flags worked out per row). The wait is bounded (1 s): on expiry SB_DEV_TIMEOUT_DISPATCH is
  * OR-ed into *dev_status and the kernel winds down. recv_rows [N * capacity, D] is this rank's receive
  * buffer, row_slot the owner layout's row_token. Padding-only groups of 32 rows are not stored.
  * Every rank must launch it once per step (an owner without rows still has rows to push).
  */
 int32_t sb_ep_dispatch_segments(int32_t capacity);
+int64_t sb_ep_dispatch_schedule_ints(int64_t num_row_blocks);
 int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t experts_local, int32_t capacity,
                        int32_t ffn_blocks, int32_t block_size, int32_t max_row_blocks, int32_t* tokens_per_expert,
                        int32_t* padded_offsets, int32_t* row_token, int32_t* copy_row, int32_t* row_block_expert,

@@ -466,8 +466,9 @@ def ep_owner_layout(recv_counts: torch.Tensor, capacity: int, ffn_dim: int, bloc
                     arrival_order: bool = False) -> list[torch.Tensor]:
     """The owner's layout over its N * capacity receive slots from the exchanged counts [N, E_local] alone: the
     eight arrays build_topology_cuda returns for ep_slot_experts' output, in one launch (error always 0). With
-    arrival_order a ninth array follows: the row blocks in the order their rows become complete when every
-    source fills its slots from the front (what ep_sdd_dispatch walks)."""
+    arrival_order a ninth array follows, the schedule ep_sdd_dispatch walks: the row blocks in the order their
+    rows become complete when every source fills its slots from the front, then 64 ints per row block (how many
+    arrival flags its rows depend on, and which)."""
     lib = _lib.load()
     _check(recv_counts.is_cuda and recv_counts.dtype == torch.int32 and recv_counts.dim() == 2 and
            recv_counts.is_contiguous(), "recv_counts must be a contiguous [N, E_local] int32 CUDA tensor")
@@ -480,7 +481,7 @@ def ep_owner_layout(recv_counts: torch.Tensor, capacity: int, ffn_dim: int, bloc
     with torch.cuda.device(recv_counts.device):
         sizes = [experts_local, experts_local + 1, max_rows, n, max_rb, max_rb + 1, max_rb * ffn_blocks, 1]
         if arrival_order:
-            sizes.append(max_rb)
+            sizes.append(int(lib.sb_ep_dispatch_schedule_ints(max_rb)))
         parts = list(torch.split(torch.empty(sum(sizes), dtype=torch.int32, device=recv_counts.device), sizes))
         order = parts.pop() if arrival_order else None
         error = parts[7]
@@ -535,7 +536,8 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
     _check(expert_offsets.numel() == num_ranks * experts_local + 1, "expert_offsets must have E + 1 entries")
     if row_block_order is not None:
         _check_index(row_block_order, "row_block_order")
-        _check(row_block_order.numel() == num_row_blocks, "row_block_order must have one entry per row block")
+        _check(row_block_order.numel() == lib.sb_ep_dispatch_schedule_ints(num_row_blocks),
+               "row_block_order must be ep_owner_layout's schedule for the same layout")
     segments = ep_dispatch_segments(capacity)
     _check(my_flags.numel() >= num_ranks * segments and done.numel() >= num_ranks * segments,
            "flags and counters need ranks * ep_dispatch_segments(capacity) entries")

@@ -48,6 +48,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "sb_ep_push_counts": (c_int, [_P, _P, c_int32, c_int32, c_int32, _P]),
     "sb_ep_barrier": (c_int, [_P, _P, _P, c_int32, c_int32, _P, _P]),
     "sb_ep_dispatch_segments": (c_int32, [c_int32]),
+    "sb_ep_dispatch_schedule_ints": (c_int64, [c_int64]),
     "sb_ep_owner_layout": (c_int, [_P, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                    _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_ep_push_rows_flagged": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, _P]),

@@ -20,8 +20,10 @@
 //               form (no global read). An asynchronous mbarrier arrive reports completion, so the
 //               threads run the full pipeline depth ahead without ever waiting for their data.
 //   warps 14-19 expert-parallel dispatch instance of SDD only (kDispatch): this rank's pushes as a source
-//               of token rows, while the gather warps first wait, per tile, for the tile's expert to
-//               have arrived from every source rank (ep_dispatch.cuh).
+//               of token rows (ep_dispatch.cuh).
+//   warp 20     dispatch instance only: waits, ahead of the gather warps, for the 256-row segments each
+//               tile's rows lie in to have arrived, and counts the complete tiles in shared memory; the
+//               gather warps start a tile when that count covers it. Tiles follow the arrival order.
 //
 // Shared-memory stage layout (all 1024-byte aligned, as the 128-byte swizzle needs):
 //   A: 128 rows x 128 B; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)      (16 KB)
@@ -102,7 +104,8 @@ struct GemmConfig {
   static constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
   static constexpr int kPushWarps = kDispatch ? 6 : 0;
   static constexpr int kFirstPushWarp = kFirstGatherWarp + kGatherWarps;
-  static constexpr int kThreads = 32 * (kFirstPushWarp + kPushWarps);
+  static constexpr int kArrivalWarp = kFirstPushWarp + kPushWarps;  // dispatch instance only
+  static constexpr int kThreads = 32 * (kArrivalWarp + (kDispatch ? 1 : 0));
   static_assert(!kDispatch || kOp == GemmOp::kSdd, "only SDD has a dispatch instance");
   static constexpr int kTmemColumns = 2 * kTileN;              // two accumulators; 256 or 512
   static constexpr int kBarrierBytes = 256;
@@ -153,10 +156,13 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t acc_empty_bar = acc_full_bar + 16;                // [2]
   const uint32_t tmem_slot = acc_empty_bar + 16;                   // uint32
   const uint32_t abort_slot = tmem_slot + 4;                       // uint32
+  const uint32_t arrived_slot = abort_slot + 4;                    // uint32, dispatch instance
   // Generic pointers to the two words the threads read directly.
   uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
   volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
   volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(smem_aligned + (abort_slot - smem_base));
+  // Dispatch instance: how many of this CTA's tiles (in walk order) have all their rows in the receive buffer.
+  uint32_t* arrived_word = reinterpret_cast<uint32_t*>(smem_aligned + (arrived_slot - smem_base));
 
   const int warp = static_cast<int>(threadIdx.x >> 5);
   const int lane = static_cast<int>(threadIdx.x & 31);
@@ -171,6 +177,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::mbar_init(acc_empty_bar + 8 * a, 32 * Cfg::kEpilogueWarps);
     }
     *abort_word = 0u;
+    *arrived_word = 0u;
     ptx::fence_barrier_init();
     if (!kIsSdd) ptx::prefetch_tensormap(&map_a);
     if (!kIsSdd && p.skip_padding) ptx::prefetch_tensormap(&map_a_rows32);
@@ -496,8 +503,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       load_tokens(tile, tok);
       cur = load_tile_info(tile);
     }
-    // Dispatch instance: the value the arrival flags carry in this step.
-    const uint32_t dispatch_epoch = kDispatch ? *p.dispatch.epoch_word : 0u;
+    uint32_t tiles_done = 0;  // dispatch instance: this CTA's tiles before the current one
     while (ok && tile < total_tiles) {
       // The next tile's record and row -> token table are fetched while this tile is gathered.
       const int32_t next = tile + tile_step;
@@ -509,13 +515,12 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       const bool live = cur.begin != cur.end;
       cur = next_info;
-      if (kDispatch && live) {
-        // The rows of this tile (tok[] holds their receive slots) may still be on their way.
-        if (!wait_rows_arrived(p.dispatch, tok, dispatch_epoch, abort_word)) {
-          if (lane == 0) give_up(SB_DEV_TIMEOUT_DISPATCH);
-          break;
-        }
-        __syncwarp();
+      if (kDispatch) {
+        // The rows of this tile may still be on their way: the arrival warp (below) watches the flags, several
+        // tiles ahead, and counts the tiles that are complete in shared memory.
+        while (ptx::ld_acquire_cta_u32(arrived_word) <= tiles_done && *abort_word == 0u) __nanosleep(20);
+        if (*abort_word != 0u) break;
+        ++tiles_done;
       }
       if (live) {
         const __nv_bfloat16* src[8];
@@ -544,14 +549,51 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tile = next;
     }
     ptx::cp_async_wait_all();
+  } else if (kDispatch && warp == Cfg::kArrivalWarp) {
+    // ---------------------------------------------------------------- dispatch arrivals (this rank as an owner)
+    // Walks this CTA's tiles in order and waits, bounded, until the arrival flags of each tile's rows carry this
+    // step's epoch; then raises the count the gather warps watch. The acquire loads that take a trip to L2 each are
+    // thereby off the gather warps' path: once the rows are in, this warp is tiles ahead.
+    const uint32_t dispatch_epoch = *p.dispatch.epoch_word;
+    uint32_t tiles_done = 0;
+    for (int32_t tile = blockIdx.x; tile < total_tiles; tile += tile_step) {
+      const int32_t rb = row_block_of(tile);
+      bool arrived = true;
+      if (__ldg(p.row_offsets + rb) != __ldg(p.row_offsets + rb + 1)) {
+        if (p.dispatch.row_block_order != nullptr) {
+          const int32_t* list = p.dispatch.row_block_order + p.num_row_blocks + static_cast<int64_t>(rb) * kWaitStride;
+          const int32_t count = __ldg(list);
+          const int32_t flag_a = lane < count ? __ldg(list + 1 + lane) : 0;
+          const int32_t flag_b = lane + 32 < count ? __ldg(list + 33 + lane) : 0;
+          arrived = wait_list_arrived(p.dispatch, count, flag_a, flag_b, dispatch_epoch, lane, abort_word);
+        } else {
+          // No schedule: the flags are worked out from the rows' receive slots, 4 rows per lane.
+          const int32_t* rows = p.row_token + static_cast<int64_t>(rb) * Cfg::kTileM;
+          int32_t slot[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) slot[j] = j < 4 ? __ldg(rows + j * 32 + lane) : -1;
+          arrived = wait_rows_arrived(p.dispatch, slot, dispatch_epoch, abort_word);
+        }
+      }
+      if (!arrived) {
+        if (lane == 0) give_up(SB_DEV_TIMEOUT_DISPATCH);
+        break;
+      }
+      __syncwarp();  // every lane's acquire before the count
+      ++tiles_done;
+      if (lane == 0) ptx::st_release_cta_u32(arrived_word, tiles_done);
+    }
   } else if (kDispatch) {
     // ---------------------------------------------------------------- dispatch pushes (this rank as a source)
-    // Chunk c of the push plan goes to worker c mod (6 * grid): consecutive chunks to different thread
-    // blocks, so that the pairs every owner needs first are complete first. These warps wait for
-    // nothing and run to the end of their list even if another role of the block has given up.
+    // Chunk position c of the slot-major walk goes to worker c mod (6 * grid): consecutive chunks to
+    // different thread blocks, so that the segments every owner needs first are complete first. These warps
+    // wait for nothing and run to the end of their list even if another role of the block has given up.
     const int push_warp = warp - Cfg::kFirstPushWarp;
-    push_chunks(p.dispatch, push_warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
-                Cfg::kPushWarps * static_cast<int>(gridDim.x), lane);
+    // Fewer warps than there are finish the early chunks sooner (less queueing on the link) at a lower total rate.
+    const int active = min(max(p.dispatch.push_warps, 1), Cfg::kPushWarps);
+    if (push_warp < active)
+      push_chunks(p.dispatch, push_warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
+                  active * static_cast<int>(gridDim.x), lane);
   }
 
   // Common exit: every role is done (or has given up); release TMEM.

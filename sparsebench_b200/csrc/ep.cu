@@ -270,6 +270,10 @@ int sb_ep_push_rows(const void* src, const int32_t* index, void* const* peer_bas
 
 int32_t sb_ep_dispatch_segments(int32_t capacity) { return capacity > 0 ? sb::dispatch_segments(capacity) : 0; }
 
+int64_t sb_ep_dispatch_schedule_ints(int64_t num_row_blocks) {
+  return num_row_blocks > 0 ? sb::dispatch_schedule_ints(num_row_blocks) : 0;
+}
+
 int sb_ep_push_rows_flagged(const void* x, const int32_t* sorted_token, const int32_t* expert_offsets,
                             void* const* peer_recv,
                             uint32_t* const* peer_flags, uint32_t* done, const uint32_t* epoch_word, int32_t my_rank,

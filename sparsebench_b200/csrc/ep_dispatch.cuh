@@ -34,6 +34,16 @@ constexpr int kPushChunkRows = 8;
 constexpr int kSegmentRows = 256;  // rows per arrival flag
 constexpr int kSegmentChunks = kSegmentRows / kPushChunkRows;
 
+// The owner's schedule (sb_ep_owner_layout writes it): after the num_row_blocks entries of the arrival order, one
+// wait list of kWaitStride ints per row block: [0] = how many flags its rows depend on, [1 ...] = their indices
+// into the owner's flag array (source * segments + segment). A row block of at most 256 rows touches at most two
+// segments per source, so the list holds up to 31 sources.
+constexpr int kWaitStride = 64;
+constexpr int kMaxDispatchRanks = (kWaitStride - 1) / 2;
+__host__ __device__ inline int64_t dispatch_schedule_ints(int64_t num_row_blocks) {
+  return num_row_blocks * (1 + kWaitStride);
+}
+
 // Arrival flags (and the sender's chunk counters) per rank pair: one per segment of the capacity.
 __host__ __device__ inline int32_t dispatch_segments(int32_t capacity) {
   return (capacity + kSegmentRows - 1) / kSegmentRows;
@@ -49,7 +59,8 @@ struct DispatchParams {
   uint32_t* done;                 // [N * segments] chunk counters of this rank, zero between kernels
   // Owner side.
   const uint32_t* my_flags;       // [N * segments], flag [s][g]: rows g*256 .. of source s are here
-  const int32_t* row_block_order; // [num_row_blocks] row blocks in the order to work on them, or null
+  const int32_t* row_block_order; // the owner's schedule: [num_row_blocks] row blocks in the order to work on them,
+                                  // then [num_row_blocks][kWaitStride] wait lists; or null (layout order, per-row waits)
   // Both: the word whose current value is this step's epoch (the exchange's barrier counter).
   const uint32_t* epoch_word;
   int32_t my_rank;
@@ -58,6 +69,7 @@ struct DispatchParams {
   int32_t capacity;
   int32_t segments;               // dispatch_segments(capacity)
   int32_t vecs_per_row;           // D * 2 / 16
+  int32_t push_warps;             // push warps per thread block that take part (inside the SDD kernel)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
@@ -70,7 +82,10 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys_u32(const uint32_t* p) {
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void fence_acquire_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ void st_relaxed_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -149,7 +164,7 @@ __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker
       copy_row_warp(dp.x + static_cast<int64_t>(token) * dp.vecs_per_row, dst + static_cast<int64_t>(r) * dp.vecs_per_row,
                     dp.vecs_per_row, lane);
     }
-    __threadfence_system();  // this lane's rows are in the destination's memory before the count below
+    fence_acq_rel_sys();  // this lane's rows are in the destination's memory before the count below
     __syncwarp();
     if (lane == 0) {
       const int32_t g = c / kSegmentChunks;
@@ -157,9 +172,10 @@ __device__ __forceinline__ void push_chunks(const DispatchParams& dp, int worker
       const uint32_t chunks = static_cast<uint32_t>((seg_rows + kPushChunkRows - 1) / kPushChunkRows);
       uint32_t* counter = dp.done + d * dp.segments + g;
       if (atomicAdd(counter, 1u) + 1u == chunks) {
-        *counter = 0u;            // ready for the next step
-        __threadfence_system();   // the other chunks' rows (fenced before their counts) before the flag
-        st_release_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.segments + g, epoch);
+        *counter = 0u;        // ready for the next step
+        fence_acq_rel_sys();  // the other chunks' rows (fenced before their counts) before the flag: with the
+                              // relaxed store below this is the release pattern
+        st_relaxed_sys_u32(dp.peer_flags[d] + dp.my_rank * dp.segments + g, epoch);
       }
     }
   }
@@ -192,8 +208,29 @@ __device__ __forceinline__ bool wait_rows_arrived(const DispatchParams& dp, cons
     }
     __nanosleep(100);
   }
-  fence_acquire_sys();
+  fence_acq_rel_sys();
   return true;
+}
+
+// The same from a row block's wait list: lane i watches the list's flags i and i + 32 with acquire loads, all lanes
+// at once (one round trip instead of one per flag, and no fence: the fence above also waits for everything this SM
+// has in flight, about 12 us per tile next to a running matmul). The caller's __syncwarp() after it carries the
+// lanes' acquires over to the whole warp.
+__device__ __forceinline__ bool wait_list_arrived(const DispatchParams& dp, int32_t count, int32_t flag_a, int32_t flag_b,
+                                                  uint32_t epoch, int lane, const volatile uint32_t* abort) {
+  const uint32_t* a = lane < count ? dp.my_flags + flag_a : nullptr;
+  const uint32_t* b = lane + 32 < count ? dp.my_flags + flag_b : nullptr;
+  const uint64_t start = dispatch_timer_ns();
+  for (uint32_t poll = 0;; ++poll) {
+    if (a != nullptr && static_cast<int32_t>(ld_acquire_sys_u32(a) - epoch) >= 0) a = nullptr;
+    if (b != nullptr && static_cast<int32_t>(ld_acquire_sys_u32(b) - epoch) >= 0) b = nullptr;
+    if (__all_sync(0xffffffffu, a == nullptr && b == nullptr)) return true;
+    if ((poll & 31u) == 31u) {
+      const bool stop = *abort != 0u || dispatch_timer_ns() - start > 1000ull * 1000ull * 1000ull;
+      if (__any_sync(0xffffffffu, stop)) return false;
+    }
+    __nanosleep(100);
+  }
 }
 
 }  // namespace sb

@@ -11,6 +11,16 @@
 namespace sb {
 namespace ptx {
 
+// CTA-scope release / acquire on a word of shared memory reached through a generic pointer.
+__device__ __forceinline__ uint32_t ld_acquire_cta_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -28,6 +28,7 @@
 
 #include <atomic>
 
+#include "ep_dispatch.cuh"
 #include "sb_common.cuh"
 
 namespace sb {
@@ -537,10 +538,11 @@ route_scatter_layout_kernel(const index_t* __restrict__ expert_idx, int64_t n, i
 // launch. Every block recomputes the small tables in shared memory and takes a share of the rows.
 // Needs N * E_local <= 1024 (one thread per (source, expert) pair).
 //
-// row_block_order (optional): the row blocks sorted by when their rows are complete if every source fills
-// its slots from the front at the same pace, i.e. by the largest slot index i among the block's rows (ties
-// in layout order, blocks without rows last). Block 0 computes the keys into shared memory and ranks them
-// by counting (at most 4096 row blocks: a few hundred in practice).
+// row_block_order (optional): the owner's schedule for a dispatch that is still in flight (ep_dispatch.cuh).
+// First the row blocks sorted by when their rows are complete if every source fills its slots from the front
+// at the same pace, i.e. by the largest slot index i among the block's rows (ties in layout order, blocks
+// without rows last); then, per row block, the arrival flags its rows wait for. Block 0 computes the keys
+// into shared memory and ranks them by counting (at most 4096 row blocks: a few hundred in practice).
 constexpr int kOwnerThreads = 1024;
 constexpr int kMaxOrderedRowBlocks = 4096;
 
@@ -626,9 +628,12 @@ ep_owner_layout_kernel(const int32_t* __restrict__ recv_counts, int32_t num_rank
   fill_layout(offsets, counts, experts_local, block_size, ffn_blocks, max_row_blocks, layout, warp_index, warp_count,
               lane);
   if (row_block_order == nullptr || blockIdx.x != 0) return;
+  const int32_t segments = dispatch_segments(capacity);
   for (int32_t rb = tid; rb < max_row_blocks; rb += kOwnerThreads) {
     const int32_t first = rb * block_size;
     int32_t key = INT32_MAX;
+    int32_t* wait_list = row_block_order + max_row_blocks + static_cast<int64_t>(rb) * kWaitStride;
+    int32_t waits = 0;
     if (first < offsets[experts_local]) {
       int32_t lo = 0, hi = experts_local;  // the expert e with offsets[e] <= first < offsets[e + 1]
       while (hi - lo > 1) {
@@ -642,9 +647,16 @@ ep_owner_layout_kernel(const int32_t* __restrict__ recv_counts, int32_t num_rank
         const int32_t run = row_start[src * experts_local + e];
         const int32_t from = max(first, run);
         const int32_t to = min(end, run + kept[src * experts_local + e]);
-        if (from < to) key = max(key, slot_start[src * experts_local + e] + (to - 1 - run));
+        if (from >= to) continue;
+        const int32_t first_slot = slot_start[src * experts_local + e] + (from - run);
+        const int32_t last_slot = slot_start[src * experts_local + e] + (to - 1 - run);
+        key = max(key, last_slot);
+        // The flags this block's rows from `src` wait for (consecutive segments of its block of slots).
+        for (int32_t g = first_slot / kSegmentRows; g <= last_slot / kSegmentRows && waits < kWaitStride - 1; ++g)
+          wait_list[++waits] = src * segments + g;
       }
     }
+    wait_list[0] = waits;
     arrival_key[rb] = key;
   }
   __syncthreads();
@@ -930,9 +942,11 @@ int sb_ep_owner_layout(const int32_t* recv_counts, int32_t num_ranks, int32_t ex
                        int32_t* row_offsets, int32_t* col_indices, int32_t* row_block_order, int32_t* error,
                        sb_stream_t stream) {
   sb::clear_error();
-  if (row_block_order != nullptr && max_row_blocks > sb::kMaxOrderedRowBlocks)
-    return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: the arrival order is built for at most %d row blocks, not %d",
-                    sb::kMaxOrderedRowBlocks, max_row_blocks);
+  if (row_block_order != nullptr && (max_row_blocks > sb::kMaxOrderedRowBlocks || num_ranks > sb::kMaxDispatchRanks ||
+                                     block_size > sb::kSegmentRows))
+    return sb::fail(SB_ERR_INVALID_ARGUMENT,
+                    "ep_owner_layout: the schedule is built for at most %d row blocks of at most %d rows and %d ranks",
+                    sb::kMaxOrderedRowBlocks, sb::kSegmentRows, sb::kMaxDispatchRanks);
   if (num_ranks <= 0 || experts_local <= 0 || static_cast<int64_t>(num_ranks) * experts_local > sb::kMaxExperts)
     return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: need 0 < ranks * local experts <= %d", sb::kMaxExperts);
   if (capacity <= 0 || ffn_blocks <= 0) return sb::fail(SB_ERR_INVALID_ARGUMENT, "ep_owner_layout: capacity and ffn_blocks must be positive");

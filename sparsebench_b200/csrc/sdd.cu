@@ -100,8 +100,10 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
   clear_error();
   if (!x || !sorted_token || !expert_offsets || !peer_recv || !peer_flags || !my_flags || !done || !epoch_word)
     return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: NULL buffer");
-  if (num_ranks <= 0 || num_ranks > 32 || my_rank < 0 || my_rank >= num_ranks || experts_local <= 0 || capacity <= 0)
-    return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: need 0 <= rank < ranks <= 32, local experts > 0, capacity > 0");
+  if (num_ranks <= 0 || num_ranks > kMaxDispatchRanks || my_rank < 0 || my_rank >= num_ranks || experts_local <= 0 ||
+      capacity <= 0)
+    return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: need 0 <= rank < ranks <= %d, local experts > 0, capacity > 0",
+                kMaxDispatchRanks);
   if (!aligned16(x)) return fail(SB_ERR_INVALID_ARGUMENT, "ep_sdd_dispatch: x must be 16-byte aligned");
   DispatchParams dp{};
   dp.x = static_cast<const uint4*>(x);
@@ -118,6 +120,8 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
   dp.experts_local = experts_local;
   dp.capacity = capacity;
   dp.segments = dispatch_segments(capacity);
+  dp.push_warps = 6;
+  if (const char* v = std::getenv("SB_PUSH_WARPS")) dp.push_warps = std::atoi(v);
   dp.vecs_per_row = d_model / 8;
   return sdd_launch(recv_rows, w1, row_slot, row_block_expert, row_offsets, h_blocks,
                     static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, nullptr,

@@ -133,3 +133,19 @@ def arrival_order(row_token: np.ndarray, capacity: int, block_size: int) -> np.n
     within = np.where(rows >= 0, rows % capacity, -1)
     keys = np.where((rows >= 0).any(axis=1), within.max(axis=1), np.iinfo(np.int32).max)
     return np.argsort(keys, kind="stable").astype(np.int32)
+
+
+def arrival_waits(row_token: np.ndarray, capacity: int, block_size: int, segment_rows: int = 256) -> list[list[int]]:
+    """numpy restatement of the wait lists in sb_ep_owner_layout's schedule: per row block the arrival flags
+    (source * segments + segment) its rows lie in, sources ascending, segments ascending within a source."""
+    segments = -(-capacity // segment_rows)
+    lists = []
+    for rows in np.asarray(row_token, dtype=np.int64).reshape(-1, block_size):
+        real = rows[rows >= 0]
+        source, within = real // capacity, real % capacity
+        flags: list[int] = []
+        for src in np.unique(source):
+            slots = within[source == src]
+            flags.extend(int(src) * segments + g for g in range(int(slots.min()) // segment_rows, int(slots.max()) // segment_rows + 1))
+        lists.append(flags)
+    return lists

@@ -97,15 +97,18 @@ def main_full(rank: int, world: int, local: int, mode: str) -> None:
     # All experts on the host for the oracle (per-expert seeds: identical on every rank); this rank's on its GPU.
     w1_all = _weights(0, range(experts), cfg.d_model, cfg.ffn_dim, 0, torch.bfloat16)
     w2_all = _weights(1, range(experts), cfg.ffn_dim, cfg.d_model, 0, torch.bfloat16)
+    overlapped = mode != "peer_nodispatch"
     if mode == "bench":
-        micro_batches, fuse, exchange = bench_ep.DEFAULT_MICRO_BATCHES.get(world, 1), True, "peer"
+        (overlapped, micro_batches), fuse, exchange = bench_ep.DEFAULT_EP_FORM.get(world, (False, 1)), True, "peer"
+    elif mode == "bench_overlapped":
+        micro_batches, fuse, exchange = 1, True, "peer"
     else:
         exchange = "peer" if mode.startswith("peer") else mode
         micro_batches = int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1
         fuse = mode != "peer_unfused"
     layer = ExpertParallelMoE(w1_all[mine.start:mine.stop].cuda(), w2_all[mine.start:mine.stop].cuda(), experts,
                               capacity=tokens * k, exchange=exchange, fuse_return=fuse, micro_batches=micro_batches,
-                              fuse_dispatch=mode != "peer_nodispatch")
+                              fuse_dispatch=overlapped)
 
     def batch(shift: int):
         """Rank r's tokens as the benchmark draws them (token seed r + shift, weights and Zipf order seed 0)."""

@@ -222,8 +222,14 @@ def test_owner_layout_from_counts_equals_routing_of_the_slots(ranks: int, expert
     for name, a, b in zip(names, with_order, got):
         assert torch.equal(a, b), name
     want_order = ep_cpu_ops.arrival_order(oracle.row_token, capacity, 128)
-    assert np.array_equal(with_order[8].cpu().numpy(), want_order)
-    assert sorted(want_order.tolist()) == list(range(len(want_order)))
+    schedule = with_order[8].cpu().numpy()
+    blocks = len(want_order)
+    assert schedule.size == _C._lib.load().sb_ep_dispatch_schedule_ints(blocks) == blocks * 65
+    assert np.array_equal(schedule[:blocks], want_order)
+    assert sorted(want_order.tolist()) == list(range(blocks))
+    lists = schedule[blocks:].reshape(blocks, 64)
+    for rb, want in enumerate(ep_cpu_ops.arrival_waits(oracle.row_token, capacity, 128)):
+        assert lists[rb, 0] == len(want) and lists[rb, 1: 1 + len(want)].tolist() == want, rb
 
 
 def _C_segments(capacity: int) -> int:

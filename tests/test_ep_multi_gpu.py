@@ -1,8 +1,8 @@
 """Expert-parallel parity on the benchmark's own shape, on as many GPUs as this machine has.
 
 Launches tests/ep_multi_gpu.py under torchrun for N = 2, 4 and 8 ranks (skipped where the machine has
-fewer GPUs): E=128 experts, D=F=2048, T=4096 tokens per rank, permuted-Zipf routing, capacity T*k, the
-micro-batch count and the fused DSD return leg the benchmark uses at that N. Every rank checks its own
+fewer GPUs): E=128 experts, D=F=2048, T=4096 tokens per rank, permuted-Zipf routing, capacity T*k, in the
+form the benchmark uses at that N and with the dispatch overlapped inside the owner's SDD kernel. Every rank checks its own
 4096 output rows against the fp32 oracle on its tokens with all 128 experts (rtol = atol = 2e-2), eagerly
 and through a replayed CUDA graph with new tokens and routing, and the owner's layout against the
 single-process layout of the concatenated batch.
@@ -39,11 +39,14 @@ def _launch(world: int, mode: str, size: str, timeout_s: int = 900) -> str:
     return text
 
 
+@pytest.mark.parametrize("form", ["bench", "bench_overlapped"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_benchmark_shape_matches_oracle_on_every_rank(world: int) -> None:
+def test_benchmark_shape_matches_oracle_on_every_rank(world: int, form: str) -> None:
+    # "bench": the form the benchmark runs at this rank count; "bench_overlapped": the dispatch inside the owner's
+    # SDD kernel, whole step, whatever the benchmark's default is.
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs, this machine has {torch.cuda.device_count()}")
-    text = _launch(world, "bench", "full")
+    text = _launch(world, form, "full")
     for rank in range(world):
         assert f"rank {rank}/{world}: expert-parallel parity ok" in text, text[-3000:]
 
