@@ -593,7 +593,7 @@ def run_profile(args: argparse.Namespace) -> None:
         logits = torch.randn(cfg.num_tokens, cfg.num_experts, generator=g).to("cuda:0")
         scores = torch.softmax(logits, dim=-1)
         for _ in range(3):
-            moe_forward_from_logits(dev.x, logits, dev.w1, dev.w2, k=cfg.k)   # router fused into routing
+            moe_forward_from_logits(dev.x, logits, dev.w1, dev.w2, k=cfg.k, one_launch_routing=True)  # router inside routing
             route(logits, cfg.k)                                             # the router as a kernel of its own
             moe_forward_rounded(dev.x, scores, dev.w1, dev.w2, k=cfg.k)      # rounding, assignment list, scatter-add combine
         torch.cuda.synchronize()

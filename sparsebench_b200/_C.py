@@ -230,16 +230,17 @@ def router_topk_cuda(logits: torch.Tensor, k: int, index_dtype: torch.dtype = to
     return idx, weight
 
 
-def route_from_logits_cuda(logits: torch.Tensor, k: int, ffn_dim: int, block_size: int):
+def route_from_logits_cuda(logits: torch.Tensor, k: int, ffn_dim: int, block_size: int, one_launch: bool = False):
     """(expert_idx [T, k] int64, expert_weight [T, k], the eight arrays of build_topology_cuda) from router
-    logits [T, E]. One kernel launch where the fused form applies (k in {1, 2, 4, 8}, E <= 256, T*k <= 32768),
-    otherwise router_topk_cuda followed by build_topology_cuda: same results either way."""
+    logits [T, E]: router_topk_cuda followed by build_topology_cuda (6 + 10 us at T=4096, E=64 on a B200), or with
+    one_launch a single kernel where that form applies (k in {1, 2, 4, 8}, E <= 1024, T*k <= 32768; 36 us there:
+    the top-k then runs on the few thread blocks of the routing cluster). Same results either way."""
     lib = _lib.load()
     _check(logits.is_cuda and logits.dim() == 2 and logits.is_contiguous(), "logits must be a contiguous [T, E] CUDA tensor")
     _check(logits.dtype in (torch.bfloat16, torch.float32), "logits must be bfloat16 or float32")
     num_tokens, num_experts = logits.shape
     _check(0 < k <= num_experts, f"need [T, E] logits with 0 < k <= E, got {tuple(logits.shape)} and k={k}")
-    if num_tokens == 0 or not lib.sb_route_from_logits_fused(num_tokens, k, num_experts):
+    if not one_launch or num_tokens == 0 or not lib.sb_route_from_logits_fused(num_tokens, k, num_experts):
         idx, weight = router_topk_cuda(logits, k)
         return idx, weight, build_topology_cuda(idx, num_experts, ffn_dim, block_size)
     n = num_tokens * k

@@ -61,17 +61,18 @@ def moe_forward(
 
 
 def moe_forward_from_logits(x: torch.Tensor, router_logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
-                            k: int = 2, mark: Callable[[str], None] = _no_mark) -> torch.Tensor:
+                            k: int = 2, mark: Callable[[str], None] = _no_mark, one_launch_routing: bool = False
+                            ) -> torch.Tensor:
     """moe_forward with the router in front: router_logits [T, E] -> top-k experts and a softmax over the k
-    picked logits (reference: sparsebench/reference.py:19-29), then the layer. The router is part of the
-    routing kernel (one launch from logits to layout), so the layer stays at four launches and the host
-    never sees an expert id."""
+    picked logits (reference: sparsebench/reference.py:19-29), then the layer. Five launches; with
+    one_launch_routing the router runs inside the routing kernel and the layer stays at four (slower as measured:
+    see route_and_layout). The host never sees an expert id."""
     num_experts, d_model, ffn_dim = w1.shape
     if w2.shape != (num_experts, ffn_dim, d_model):
         raise ValueError(f"w2 must be {(num_experts, ffn_dim, d_model)}, got {tuple(w2.shape)}")
     if x.shape[1] != d_model or router_logits.shape != (x.shape[0], num_experts):
         raise ValueError("x must be [T, D] and router_logits [T, E]")
-    _, expert_weight, topo = route_and_layout(router_logits, k, ffn_dim, BLOCK_SIZE)
+    _, expert_weight, topo = route_and_layout(router_logits, k, ffn_dim, BLOCK_SIZE, one_launch_routing)
     mark("routing")
     h = sdd(x, w1, topo, gelu=True, skip_padding_rows=True, layout_from_routing=True)
     mark("SDD + GELU (fused)")

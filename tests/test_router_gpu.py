@@ -111,13 +111,14 @@ def test_rejects_bad_input() -> None:
 
 # ---- router fused into the routing kernel: logits -> layout in one launch ----------------------------------
 
+@pytest.mark.parametrize("one_launch", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize(("num_tokens", "num_experts", "k", "block_size"),
                          [(1, 4, 2, 16), (13, 8, 1, 4), (513, 8, 2, 128), (4096, 64, 2, 128), (1000, 256, 4, 128),
                           (300, 33, 8, 16), (16384, 128, 2, 128), (77, 64, 3, 128), (20000, 64, 2, 128), (64, 300, 2, 128)])
-def test_route_and_layout_equals_router_then_routing(num_tokens, num_experts, k, block_size, dtype) -> None:
-    # Covers the one-launch form (k a power of two, E <= 256, T*k <= 32768) and the shapes that fall back to two
-    # launches (k = 3, T*k > 32768, E > 256): identical results either way, and identical to the oracle.
+def test_route_and_layout_equals_router_then_routing(num_tokens, num_experts, k, block_size, dtype, one_launch) -> None:
+    # Covers the one-launch form (k a power of two, T*k <= 32768), the shapes that fall back to two launches even
+    # when it is asked for (k = 3, T*k > 32768) and the default two launches: identical results, identical to the oracle.
     import numpy as np
 
     from oracle import layout as L
@@ -129,7 +130,7 @@ def test_route_and_layout_equals_router_then_routing(num_tokens, num_experts, k,
     grid = torch.linspace(-4.0, 4.0, num_experts).to(dtype)
     logits = torch.stack([grid[torch.randperm(num_experts, generator=g)] for _ in range(num_tokens)])
     ffn_dim = 2 * block_size
-    idx, weight, topo = route_and_layout(logits.cuda(), k, ffn_dim, block_size)
+    idx, weight, topo = route_and_layout(logits.cuda(), k, ffn_dim, block_size, one_launch)
     want_idx, want_weight = M.route(logits, k)
     assert idx.dtype == torch.int64 and weight.dtype == dtype
     assert torch.equal(idx.cpu(), want_idx)
@@ -141,7 +142,8 @@ def test_route_and_layout_equals_router_then_routing(num_tokens, num_experts, k,
     assert int(topo.error.item()) == 0
 
 
-def test_layer_from_logits_in_a_graph_with_new_logits() -> None:
+@pytest.mark.parametrize("one_launch", [True, False])
+def test_layer_from_logits_in_a_graph_with_new_logits(one_launch: bool) -> None:
     from sparsebench_b200 import moe_forward_from_logits
 
     g = torch.Generator().manual_seed(3)
@@ -151,16 +153,16 @@ def test_layer_from_logits_in_a_graph_with_new_logits() -> None:
     w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
     logits = torch.randn(num_tokens, num_experts, generator=g).cuda()  # fp32: no two logits of a token are equal
     stages: list[str] = []
-    moe_forward_from_logits(x, logits, w1, w2, mark=stages.append)
+    moe_forward_from_logits(x, logits, w1, w2, mark=stages.append, one_launch_routing=one_launch)
     assert stages == ["routing", "SDD + GELU (fused)", "DSD", "combine"]
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        moe_forward_from_logits(x, logits, w1, w2)
+        moe_forward_from_logits(x, logits, w1, w2, one_launch_routing=one_launch)
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        out = moe_forward_from_logits(x, logits, w1, w2)
+        out = moe_forward_from_logits(x, logits, w1, w2, one_launch_routing=one_launch)
     new_logits = torch.randn(num_tokens, num_experts, generator=g)
     logits.copy_(new_logits.cuda())
     graph.replay()
