@@ -82,7 +82,12 @@ __device__ __forceinline__ bool is_pick(const int32_t* __restrict__ picks, int64
 __global__ void __launch_bounds__(kSelectThreads, 1)
 rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restrict__ picks,
                        const int32_t* __restrict__ counts, int64_t num_tokens, int32_t num_experts, int32_t k,
-                       int32_t tile, uint8_t* __restrict__ keep) {
+                       int32_t tile, int32_t cached, uint8_t* __restrict__ keep) {
+  // With `cached` the expert's column (every token's key and whether it picked the expert) is read once into
+  // shared memory; the four select passes and the two walks after them then stay on chip. The column is strided
+  // by E in global memory, so every pass over it costs a sector per token otherwise.
+  extern __shared__ uint32_t column_keys[];                                         // [T] when cached
+  uint8_t* column_picks = reinterpret_cast<uint8_t*>(column_keys + (cached ? num_tokens : 0));  // [T]
   __shared__ int32_t histogram[256];
   __shared__ int32_t scratch[33];
   __shared__ uint32_t chosen_prefix;
@@ -103,6 +108,15 @@ rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restri
     for (int64_t t = threadIdx.x; t < num_tokens; t += kSelectThreads) keep[t * num_experts + e] = is_pick(picks, t, k, e);
     return;
   }
+  if (cached) {
+    for (int64_t t = threadIdx.x; t < num_tokens; t += kSelectThreads) {
+      column_keys[t] = order_key(__ldg(scores + t * num_experts + e));
+      column_picks[t] = is_pick(picks, t, k, e) ? 1 : 0;
+    }
+    __syncthreads();
+  }
+  auto pick_of = [&](int64_t t) { return cached ? column_picks[t] != 0 : is_pick(picks, t, k, e); };
+  auto key_of = [&](int64_t t) { return cached ? column_keys[t] : order_key(__ldg(scores + t * num_experts + e)); };
   // Radix select: the `wanted`-th largest key among the candidates, one byte per pass from the top.
   uint32_t prefix = 0, prefix_mask = 0;
   int32_t remaining = wanted;  // rank still to be found inside the current prefix class
@@ -110,8 +124,8 @@ rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restri
     for (int i = threadIdx.x; i < 256; i += kSelectThreads) histogram[i] = 0;
     __syncthreads();
     for (int64_t t = threadIdx.x; t < num_tokens; t += kSelectThreads) {
-      if (is_pick(picks, t, k, e) != shrinking) continue;
-      const uint32_t key = order_key(__ldg(scores + t * num_experts + e));
+      if (pick_of(t) != shrinking) continue;
+      const uint32_t key = key_of(t);
       if ((key & prefix_mask) == prefix) atomicAdd(&histogram[(key >> shift) & 0xffu], 1);
     }
     __syncthreads();
@@ -138,8 +152,8 @@ rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restri
   const int64_t t_end = min(num_tokens, t_begin + per_thread);
   int32_t equal_here = 0;
   for (int64_t t = t_begin; t < t_end; ++t) {
-    if (is_pick(picks, t, k, e) != shrinking) continue;
-    equal_here += order_key(__ldg(scores + t * num_experts + e)) == prefix ? 1 : 0;
+    if (pick_of(t) != shrinking) continue;
+    equal_here += key_of(t) == prefix ? 1 : 0;
   }
   // Exclusive scan of equal_here over the threads (two-level, through shared memory).
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -162,12 +176,12 @@ rounding_select_kernel(const float* __restrict__ scores, const int32_t* __restri
   __syncthreads();
   int32_t equal_before = (warp > 0 ? scratch[warp - 1] : 0) + inclusive - equal_here;
   for (int64_t t = t_begin; t < t_end; ++t) {
-    const bool pick = is_pick(picks, t, k, e);
+    const bool pick = pick_of(t);
     bool kept;
     if (pick != shrinking) {
       kept = pick;  // not a candidate: picks stay when growing, non-picks stay out when shrinking
     } else {
-      const uint32_t key = order_key(__ldg(scores + t * num_experts + e));
+      const uint32_t key = key_of(t);
       if (key > prefix) kept = true;
       else if (key < prefix) kept = false;
       else kept = equal_before++ < remaining;
@@ -318,8 +332,11 @@ int sb_token_rounding(const float* scores, int64_t num_tokens, int32_t num_exper
   if (blocks > static_cast<int64_t>(info->sm_count) * 8) blocks = static_cast<int64_t>(info->sm_count) * 8;
   rounding_topk_kernel<<<static_cast<unsigned>(blocks), kTopkThreads, 0, s>>>(scores, num_tokens, num_experts, k, picks, counts);
   if (int rc = check_launch("token_rounding (top-k)")) return rc;
-  rounding_select_kernel<<<static_cast<unsigned>(num_experts), kSelectThreads, 0, s>>>(scores, picks, counts, num_tokens,
-                                                                                      num_experts, k, tile, keep);
+  // The expert's column in shared memory (5 bytes per token) where it fits beside the static arrays.
+  const size_t column_bytes = static_cast<size_t>(num_tokens) * 5;
+  const int32_t cached = column_bytes <= 46 * 1024 ? 1 : 0;
+  rounding_select_kernel<<<static_cast<unsigned>(num_experts), kSelectThreads, cached ? column_bytes : 0, s>>>(
+      scores, picks, counts, num_tokens, num_experts, k, tile, cached, keep);
   if (int rc = check_launch("token_rounding (select)")) return rc;
   const int64_t capacity = sb_token_rounding_capacity(num_tokens, num_experts, k, tile);
   rounding_count_kernel<<<static_cast<unsigned>(blocks), kTopkThreads, 0, s>>>(scores, keep, num_tokens, num_experts,
