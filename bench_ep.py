@@ -508,7 +508,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     if fused_dispatch:
         # sort, plan, push counts, barrier, owner layout, SDD with the pushes, DSD (+ return) [, push], barrier, combine
         launches_per_step = 9 if fused_return else 10
-        dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for their expert's arrival flags"
+        dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for the arrival flags of the 256-row segments their rows lie in"
     else:
         if moe.peer is not None:
             # sort, plan, push counts, push rows, barrier, owner layout, SDD, DSD (+ return) [, push rows], barrier, combine
