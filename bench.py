@@ -632,10 +632,11 @@ def main() -> None:
     parser.add_argument("--ep-unfused-return", action="store_true",
                         help="N > 1, peer exchange: DSD writes y and a second kernel pushes it (default: the DSD "
                              "epilogue stores the rows into the source ranks' buffers)")
-    parser.add_argument("--ep-dispatch", default="auto", choices=["auto", "overlapped", "separate"],
+    parser.add_argument("--ep-dispatch", default="auto", choices=["auto", "beside", "overlapped", "separate"],
                         help="N > 1, peer exchange: 'separate' pushes all rows and waits for every rank before the "
-                             "owner's routing; 'overlapped' lets the owner's SDD kernel push the rows while its tiles "
-                             "wait for the segments they need; 'auto' takes the measured default for this N")
+                             "owner's routing; 'beside' runs the push kernel on a second stream beside the owner's SDD "
+                             "kernel, whose tiles wait for the segments they need; 'overlapped' lets extra warps of "
+                             "that SDD kernel push the rows; 'auto' takes the measured default for this N")
     parser.add_argument("--ep-unfused-dispatch", action="store_true", help="same as --ep-dispatch separate")
     parser.add_argument("--no-nccl-context", action="store_true",
                         help="N > 1: skip the few extra steps with NCCL all-to-all collectives as the exchange")

@@ -37,11 +37,11 @@ DEFAULT_MICRO_BATCHES: dict[int, int] = {n: form[1] for n, form in DEFAULT_EP_FO
 
 
 def overlapped_dispatch_wanted(args, world: int) -> bool:
-    """--ep-dispatch overlapped / separate, the older --ep-unfused-dispatch, else the table above."""
+    """--ep-dispatch beside / overlapped / separate, the older --ep-unfused-dispatch, else the table above."""
     choice = getattr(args, "ep_dispatch", "auto")
     if getattr(args, "ep_unfused_dispatch", False) or choice == "separate":
         return False
-    if choice == "overlapped":
+    if choice in ("overlapped", "beside"):
         return True
     return DEFAULT_EP_FORM.get(world, (False, 1))[0]
 
@@ -433,6 +433,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
             moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
                                     fuse_return=not getattr(args, "ep_unfused_return", False),
                                     fuse_dispatch=overlapped_dispatch_wanted(args, world),
+                                    push_beside=getattr(args, "ep_dispatch", "auto") != "overlapped",
                                     micro_batches=micro_batches)
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line
@@ -509,6 +510,10 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         # sort, plan, push counts, barrier, owner layout, SDD with the pushes, DSD (+ return) [, push], barrier, combine
         launches_per_step = 9 if fused_return else 10
         dispatch_leg = "rows pushed by the owner's SDD kernel, tiles wait for the arrival flags of the 256-row segments their rows lie in"
+        if moe.push_beside:
+            launches_per_step += 1  # the push kernel on its own stream
+            dispatch_leg = ("rows pushed by a kernel on a second stream beside the owner's SDD kernel, whose tiles wait "
+                            "for the arrival flags of the 256-row segments their rows lie in")
     else:
         if moe.peer is not None:
             # sort, plan, push counts, push rows, barrier, owner layout, SDD, DSD (+ return) [, push rows], barrier, combine
@@ -551,7 +556,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     timed_moe = moe
     if moe.micro_batches > 1:
         moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
-                                fuse_return=timed_moe.fuse_return, fuse_dispatch=timed_moe.fuse_dispatch)
+                                fuse_return=timed_moe.fuse_return, fuse_dispatch=timed_moe.fuse_dispatch,
+                                push_beside=timed_moe.push_beside)
     names: list[str] = []
     sums: dict[str, float] = {}
     iters = max(5, min(args.steps, 30))

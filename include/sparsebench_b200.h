@@ -373,6 +373,9 @@ int sb_ep_dsd_push(const void* h_blocks, int64_t num_blocks, const void* w, int6
  * OR-ed into *dev_status and the kernel winds down. recv_rows [N * capacity, D] is this rank's receive
  * buffer, row_slot the owner layout's row_token. Padding-only groups of 32 rows are not stored.
  * Every rank must launch it once per step (an owner without rows still has rows to push).
+ * push_warps: how many of the six push warps per thread block take part (-1: all). 0: none, this rank's rows
+ * are pushed by sb_ep_push_rows_flagged, launched BEFORE this kernel on another stream so that the two run side by
+ * side (the push kernel waits for nothing; this kernel's waits are bounded as above).
  */
 int32_t sb_ep_dispatch_segments(int32_t capacity);
 int64_t sb_ep_dispatch_schedule_ints(int64_t num_row_blocks);
@@ -391,7 +394,7 @@ int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const int32_t* row
                        const int32_t* expert_offsets, const int32_t* row_block_order, void* const* peer_recv,
                        uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
                        const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks, int32_t experts_local,
-                       int32_t capacity, int32_t* dev_status, sb_stream_t stream);
+                       int32_t capacity, int32_t push_warps, int32_t* dev_status, sb_stream_t stream);
 
 #ifdef __cplusplus
 }

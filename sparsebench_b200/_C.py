@@ -513,11 +513,12 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
                     row_offsets: torch.Tensor, num_nnz: int, x: torch.Tensor, sorted_token: torch.Tensor,
                     expert_offsets: torch.Tensor, row_block_order: torch.Tensor | None, peer_recv: torch.Tensor,
                     peer_flags: torch.Tensor, my_flags: torch.Tensor, done: torch.Tensor, epoch: torch.Tensor,
-                    my_rank: int, capacity: int) -> torch.Tensor:
+                    my_rank: int, capacity: int, push_warps: int = -1) -> torch.Tensor:
     """SDD + GELU over the receive buffer `recv` [N * capacity, D] whose rows are still arriving: extra warps of
     the same kernel push this rank's own rows `x[sorted_token]` to their owners, and every tile waits (bounded)
     for the 256-row segments its rows lie in. Tiles are walked in row_block_order (ep_owner_layout's arrival
-    order; None: layout order). Returns the blocks [num_nnz, 128, 128] like sdd_cuda with skip_padding_rows."""
+    order; None: layout order). push_warps = 0: this rank's rows are pushed by ep_push_rows_flagged, launched before
+    this call on another stream. Returns the blocks [num_nnz, 128, 128] like sdd_cuda with skip_padding_rows."""
     lib = _lib.load()
     _check(recv.is_cuda and w1.is_cuda and x.is_cuda and recv.device == w1.device == x.device, "all inputs on one GPU")
     _check(recv.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and x.dtype == torch.bfloat16, "rows and w1 must be bfloat16")
@@ -548,6 +549,6 @@ def ep_sdd_dispatch(recv: torch.Tensor, w1: torch.Tensor, row_slot: torch.Tensor
                                           _ptr(out), d_model, ffn_dim, num_row_blocks, _ptr(x), _ptr(sorted_token),
                                           _ptr(expert_offsets), _ptr(row_block_order) if row_block_order is not None else None,
                                           _ptr(peer_recv), _ptr(peer_flags), _ptr(my_flags), _ptr(done),
-                                          _ptr(epoch), my_rank, num_ranks, experts_local, capacity,
+                                          _ptr(epoch), my_rank, num_ranks, experts_local, capacity, push_warps,
                                           _ptr(device_status(recv.device)), _stream()))
     return out

@@ -53,7 +53,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                    _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "sb_ep_push_rows_flagged": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int32, c_int32, c_int32, c_int32, c_int32, _P]),
     "sb_ep_sdd_dispatch": (c_int, [_P, _P, _P, _P, _P, _P, c_int32, c_int32, c_int32, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                                   c_int32, c_int32, c_int32, c_int32, _P, _P]),
+                                   c_int32, c_int32, c_int32, c_int32, c_int32, _P, _P]),
     "sb_ep_dsd_push": (c_int, [_P, c_int64, _P, c_int64, c_int32, _P, _P, c_int32, _P, _P, c_int32, c_int32, c_int32,
                                _P, _P]),
 }

@@ -87,7 +87,7 @@ struct GemmParams {
   DispatchParams dispatch;
 };
 
-template <GemmOp kOp, int kTileN, bool kDispatch = false>
+template <GemmOp kOp, int kTileN, int kDispatch = 0>
 struct GemmConfig {
   static constexpr int kTileM = 128;
   static constexpr int kTileK = 64;
@@ -97,12 +97,17 @@ struct GemmConfig {
   static constexpr int kBSlabs = kTileN / 64;
   static constexpr int kBBytes = kBSlabs * kBSlabBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kTileN == 256 ? 4 : 6;
+  // Dispatch instances (expert-parallel owner whose rows are still arriving): 1 = this rank's rows are pushed by
+  // warps (loads and stores through registers), 2 = by bulk copies through a ring in shared memory that one thread
+  // drives; the ring takes the place of one pipeline stage.
+  static constexpr bool kBulkPush = kDispatch == 2;
+  static constexpr int kPushRingBytes = kBulkPush ? 48 * 1024 : 0;
+  static constexpr int kStages = kTileN == 256 ? (kBulkPush ? 3 : 4) : 6;
   static constexpr int kEpilogueWarps = 8;
   static constexpr int kGatherWarps = kOp == GemmOp::kSdd ? 4 : 0;
   static constexpr int kFirstEpilogueWarp = 2;
   static constexpr int kFirstGatherWarp = kFirstEpilogueWarp + kEpilogueWarps;
-  static constexpr int kPushWarps = kDispatch ? 6 : 0;
+  static constexpr int kPushWarps = kDispatch == 1 ? 6 : (kDispatch == 2 ? 1 : 0);
   static constexpr int kFirstPushWarp = kFirstGatherWarp + kGatherWarps;
   static constexpr int kArrivalWarp = kFirstPushWarp + kPushWarps;  // dispatch instance only
   static constexpr int kThreads = 32 * (kArrivalWarp + (kDispatch ? 1 : 0));
@@ -110,7 +115,7 @@ struct GemmConfig {
   static constexpr int kTmemColumns = 2 * kTileN;              // two accumulators; 256 or 512
   static constexpr int kBarrierBytes = 256;
   static constexpr int kStagingBytes = 32 * 128;               // per epilogue warp: 32 rows x 64 bf16
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kEpilogueWarps * kStagingBytes + kBarrierBytes;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kPushRingBytes + kEpilogueWarps * kStagingBytes + kBarrierBytes;
   static constexpr uint32_t kFullArrivals = kOp == GemmOp::kSdd ? 1 + 32 * kGatherWarps : 1;
   static constexpr uint32_t kTxBytes = kOp == GemmOp::kSdd ? kBBytes : kStageBytes;
   static_assert(kTileN == 128 || kTileN == 256, "tile width");
@@ -136,7 +141,126 @@ __device__ __forceinline__ float gelu_erf(float v) {
   return 0.5f * v * (1.0f + copysignf(erf_abs, x));
 }
 
-template <GemmOp kOp, int kTileN, bool kDispatch = false>
+// The source side of the overlapped dispatch as bulk copies, driven by ONE thread of the thread block: a chunk of
+// up to four rows is fetched from x into one of three buffers of a shared-memory ring (bulk loads counted on the
+// buffer's mbarrier) and sent from there into its owner's receive buffer (bulk stores, one bulk group per chunk).
+// No registers carry data and nothing waits for a load to come back before the next is issued, so one thread keeps
+// 48 KB per SM in flight, in order: chunk j is stored while chunks j+1 and j+2 load. A chunk is counted towards its
+// segment (ep_dispatch.cuh) once its group is complete, two chunks later, so the thread never waits for a store that
+// it has only just issued. Chunk positions are walked like push_chunks walks them (slot-major, round-robin over the
+// destinations), worker w of num_workers taking every num_workers-th. Returns false if a load did not arrive in time.
+constexpr int kBulkMaxChunkRows = 4;
+
+template <int kRingBytes>
+__device__ inline bool push_rows_bulk(const DispatchParams& dp, uint32_t ring_base, uint32_t ring_bar, int worker,
+                                      int num_workers, const volatile uint32_t* abort) {
+  constexpr int kBufferBytes = kRingBytes / 3;
+  const int32_t row_bytes = dp.vecs_per_row * 16;
+  const int32_t chunk_rows = min(kBulkMaxChunkRows, kBufferBytes / row_bytes);  // 4, 2 or 1 (the host checks >= 1)
+  const int32_t seg_chunks = kSegmentRows / chunk_rows;
+  const int32_t ranks = dp.num_ranks;
+  const int32_t total = dp.segments * seg_chunks * ranks;
+  const uint32_t epoch = *dp.epoch_word;
+  const char* x = reinterpret_cast<const char*>(dp.x);
+
+  struct Chunk { int32_t d, slot0, rows, kept, token[kBulkMaxChunkRows]; };
+  Chunk ring[16];  // descriptors of the chunks in flight: oldest not yet counted .. the one whose tokens are being read
+  int32_t next_idx = worker;
+  // The next position of this worker that holds rows; its tokens are read here and first used an iteration later.
+  auto fetch = [&](Chunk& out) {
+    for (; next_idx < total; next_idx += num_workers) {
+      const int32_t c = next_idx / ranks;
+      const int32_t d = (next_idx - c * ranks + dp.my_rank + c) % ranks;
+      const int32_t base = __ldg(dp.expert_offsets + d * dp.experts_local);
+      const int32_t kept = min(dp.capacity, __ldg(dp.expert_offsets + (d + 1) * dp.experts_local) - base);
+      const int32_t slot0 = c * chunk_rows;
+      if (slot0 >= kept) continue;
+      out.d = d; out.slot0 = slot0; out.rows = min(chunk_rows, kept - slot0); out.kept = kept;
+#pragma unroll
+      for (int r = 0; r < kBulkMaxChunkRows; ++r)
+        out.token[r] = r < out.rows ? __ldg(dp.sorted_token + base + slot0 + r) : 0;
+      next_idx += num_workers;
+      return true;
+    }
+    return false;
+  };
+  auto issue_loads = [&](int32_t j, const Chunk& ch) {
+    const uint32_t buffer = ring_base + static_cast<uint32_t>(j % 3) * kBufferBytes;
+    const uint32_t bar = ring_bar + 8u * static_cast<uint32_t>(j % 3);
+    ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(ch.rows * row_bytes));
+    for (int32_t r = 0; r < ch.rows; ++r)
+      ptx::bulk_load(buffer + static_cast<uint32_t>(r * row_bytes), x + static_cast<int64_t>(ch.token[r]) * row_bytes,
+                     static_cast<uint32_t>(row_bytes), bar);
+  };
+  // Chunks [from, to) are complete in their owners' memory: count them towards their segments. One fence for all of
+  // them, the counters' round trips side by side.
+  auto signal = [&](int32_t from, int32_t to) {
+    if (from >= to) return;
+    fence_acq_rel_sys();
+    for (int32_t j0 = from; j0 < to; j0 += 4) {
+      uint32_t before[4];
+      uint32_t* counter[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const Chunk& ch = ring[(j0 + q) & 15];
+        counter[q] = dp.done + ch.d * dp.segments + ch.slot0 / kSegmentRows;
+        if (j0 + q < to) before[q] = atomicAdd(counter[q], 1u);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (j0 + q >= to) continue;
+        const Chunk& ch = ring[(j0 + q) & 15];
+        const int32_t g = ch.slot0 / kSegmentRows;
+        const int32_t seg_rows = min(ch.kept, (g + 1) * kSegmentRows) - g * kSegmentRows;
+        if (before[q] + 1u == static_cast<uint32_t>((seg_rows + chunk_rows - 1) / chunk_rows)) {
+          *counter[q] = 0u;
+          fence_acq_rel_sys();  // the other chunks of the segment (counted after their fences) before the flag
+          st_relaxed_sys_u32(dp.peer_flags[ch.d] + dp.my_rank * dp.segments + g, epoch);
+        }
+      }
+    }
+  };
+
+  // Chunks 0 and 1 are loading, the tokens of chunk 2 are on their way, before the first store is issued.
+  int32_t fetched = 0, loading = 0;
+  for (; fetched < 3 && fetch(ring[fetched & 15]); ++fetched) {}
+  for (; loading < 2 && loading < fetched; ++loading) issue_loads(loading, ring[loading & 15]);
+  bool ok = true;
+  int32_t stored = 0, counted = 0;
+  for (; stored < loading; ++stored) {
+    const Chunk& ch = ring[stored & 15];
+    if (!ptx::mbar_wait_bounded(ring_bar + 8u * static_cast<uint32_t>(stored % 3), static_cast<uint32_t>(stored / 3) & 1u,
+                                abort)) {
+      ok = false;
+      break;
+    }
+    ptx::fence_proxy_async_shared();
+    const uint32_t buffer = ring_base + static_cast<uint32_t>(stored % 3) * kBufferBytes;
+    char* dst = reinterpret_cast<char*>(dp.peer_recv[ch.d]) +
+                (static_cast<int64_t>(dp.my_rank) * dp.capacity + ch.slot0) * row_bytes;
+    for (int32_t r = 0; r < ch.rows; ++r)
+      ptx::bulk_store(dst + static_cast<int64_t>(r) * row_bytes, buffer + static_cast<uint32_t>(r * row_bytes),
+                      static_cast<uint32_t>(row_bytes));
+    ptx::bulk_commit();
+    // The buffer of the chunk before this one is free once that chunk's group has read it.
+    ptx::bulk_wait_read_but<1>();
+    if (loading < fetched) {
+      issue_loads(loading, ring[loading & 15]);
+      ++loading;
+    }
+    if (fetched == loading && fetch(ring[fetched & 15])) ++fetched;  // tokens for the iteration after this one
+    if (stored + 1 - 2 - counted >= 4) {  // four chunks (all but the two most recent groups) wait to be counted
+      ptx::bulk_wait_but<2>();
+      signal(counted, stored - 1);
+      counted = stored - 1;
+    }
+  }
+  ptx::bulk_wait_all();  // also on the way out after a failed wait: nothing of this block may still read the ring
+  signal(counted, stored);
+  return ok;
+}
+
+template <GemmOp kOp, int kTileN, int kDispatch = 0>
 __global__ void __launch_bounds__(GemmConfig<kOp, kTileN, kDispatch>::kThreads, 1)
 bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a_rows32,
                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
@@ -148,7 +272,8 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_base = smem_base;
   const uint32_t b_base = smem_base + Cfg::kStages * Cfg::kABytes;
-  const uint32_t staging_base = smem_base + Cfg::kStages * Cfg::kStageBytes;  // 1024-byte aligned
+  const uint32_t ring_base = smem_base + Cfg::kStages * Cfg::kStageBytes;     // bulk-push instance: three chunk buffers
+  const uint32_t staging_base = ring_base + Cfg::kPushRingBytes;              // 1024-byte aligned
   const uint32_t bar_base = staging_base + Cfg::kEpilogueWarps * Cfg::kStagingBytes;
   const uint32_t full_bar = bar_base;                              // [kStages]
   const uint32_t empty_bar = bar_base + 8 * Cfg::kStages;          // [kStages]
@@ -157,6 +282,7 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t tmem_slot = acc_empty_bar + 16;                   // uint32
   const uint32_t abort_slot = tmem_slot + 4;                       // uint32
   const uint32_t arrived_slot = abort_slot + 4;                    // uint32, dispatch instance
+  const uint32_t ring_bar = (arrived_slot + 4 + 7) & ~7u;          // [3], bulk-push instance
   // Generic pointers to the two words the threads read directly.
   uint8_t* smem_aligned = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
   volatile uint32_t* tmem_word = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
@@ -178,6 +304,8 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     *abort_word = 0u;
     *arrived_word = 0u;
+    if (Cfg::kBulkPush)
+      for (int b = 0; b < 3; ++b) ptx::mbar_init(ring_bar + 8 * b, 1);
     ptx::fence_barrier_init();
     if (!kIsSdd) ptx::prefetch_tensormap(&map_a);
     if (!kIsSdd && p.skip_padding) ptx::prefetch_tensormap(&map_a_rows32);
@@ -588,12 +716,18 @@ bsr_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // Chunk position c of the slot-major walk goes to worker c mod (6 * grid): consecutive chunks to
     // different thread blocks, so that the segments every owner needs first are complete first. These warps
     // wait for nothing and run to the end of their list even if another role of the block has given up.
+    if (Cfg::kBulkPush) {
+      if (lane == 0 && !push_rows_bulk<Cfg::kPushRingBytes>(p.dispatch, ring_base, ring_bar, static_cast<int>(blockIdx.x),
+                                                           static_cast<int>(gridDim.x), abort_word))
+        give_up(SB_DEV_TIMEOUT_PRODUCER);
+    } else {
     const int push_warp = warp - Cfg::kFirstPushWarp;
     // Fewer warps than there are finish the early chunks sooner (less queueing on the link) at a lower total rate.
-    const int active = min(max(p.dispatch.push_warps, 1), Cfg::kPushWarps);
+    const int active = min(max(p.dispatch.push_warps, 0), Cfg::kPushWarps);  // 0: another launch pushes
     if (push_warp < active)
       push_chunks(p.dispatch, push_warp * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x),
                   active * static_cast<int>(gridDim.x), lane);
+    }
   }
 
   // Common exit: every role is done (or has given up); release TMEM.
@@ -630,7 +764,7 @@ inline bool weights_reused_in_l2(int32_t /*num_row_blocks*/, int32_t /*num_exper
 
 // Opt-in to the large dynamic shared memory of one kernel instance, once per device. Two host threads
 // may both find the flag clear and both set the attribute (harmless: same value); the flag itself is atomic.
-template <GemmOp kOp, int kTileN, bool kDispatch = false>
+template <GemmOp kOp, int kTileN, int kDispatch = 0>
 int prepare_gemm_kernel(int device) {
   static std::atomic<bool> done[kMaxDevices] = {};
   if (done[device].load(std::memory_order_acquire)) return SB_OK;
@@ -642,7 +776,7 @@ int prepare_gemm_kernel(int device) {
   return SB_OK;
 }
 
-template <GemmOp kOp, int kTileN, bool kDispatch = false>
+template <GemmOp kOp, int kTileN, int kDispatch = 0>
 int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_a_rows32, const CUtensorMap& map_b,
                 const CUtensorMap& map_out, const GemmParams& params, cudaStream_t stream, const char* what) {
   int device = 0;

@@ -70,6 +70,7 @@ struct DispatchParams {
   int32_t segments;               // dispatch_segments(capacity)
   int32_t vecs_per_row;           // D * 2 / 16
   int32_t push_warps;             // push warps per thread block that take part (inside the SDD kernel)
+  int32_t bulk_engine;            // host side: take the SDD instance that pushes with bulk copies instead of warps
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {

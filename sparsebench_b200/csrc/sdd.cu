@@ -69,8 +69,12 @@ int sdd_launch(const void* x, const void* w1, const int32_t* row_token, const in
   }
   if (dispatch != nullptr) {
     params.dispatch = *dispatch;
-    return launch_gemm<GemmOp::kSdd, 256, true>(map_a, map_a, map_b, map_out, params, as_stream(stream),
-                                                "sdd (dispatch)");
+    // A row must fit a third of the bulk-push ring; wider rows go through the push warps.
+    if (dispatch->bulk_engine != 0 && d_model * 2 <= GemmConfig<GemmOp::kSdd, 256, 2>::kPushRingBytes / 3)
+      return launch_gemm<GemmOp::kSdd, 256, 2>(map_a, map_a, map_b, map_out, params, as_stream(stream),
+                                               "sdd (dispatch, bulk pushes)");
+    return launch_gemm<GemmOp::kSdd, 256, 1>(map_a, map_a, map_b, map_out, params, as_stream(stream),
+                                             "sdd (dispatch)");
   }
   return launch_gemm<GemmOp::kSdd, 256>(map_a, map_a, map_b, map_out, params, as_stream(stream), "sdd");
 }
@@ -95,7 +99,8 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
                                   const int32_t* row_block_order, void* const* peer_recv,
                                   uint32_t* const* peer_flags, const uint32_t* my_flags, uint32_t* done,
                                   const uint32_t* epoch_word, int32_t my_rank, int32_t num_ranks,
-                                  int32_t experts_local, int32_t capacity, int32_t* dev_status, sb_stream_t stream) {
+                                  int32_t experts_local, int32_t capacity, int32_t push_warps, int32_t* dev_status,
+                                  sb_stream_t stream) {
   using namespace sb;
   clear_error();
   if (!x || !sorted_token || !expert_offsets || !peer_recv || !peer_flags || !my_flags || !done || !epoch_word)
@@ -120,8 +125,14 @@ extern "C" int sb_ep_sdd_dispatch(const void* recv_rows, const void* w1, const i
   dp.experts_local = experts_local;
   dp.capacity = capacity;
   dp.segments = dispatch_segments(capacity);
-  dp.push_warps = 6;
-  if (const char* v = std::getenv("SB_PUSH_WARPS")) dp.push_warps = std::atoi(v);
+  dp.push_warps = push_warps;
+  if (push_warps < 0) {
+    dp.push_warps = 6;
+    if (const char* v = std::getenv("SB_PUSH_WARPS")) dp.push_warps = std::atoi(v);
+  }
+  dp.bulk_engine = 0;
+  if (push_warps != 0)
+    if (const char* v = std::getenv("SB_PUSH_ENGINE")) dp.bulk_engine = std::atoi(v);
   dp.vecs_per_row = d_model / 8;
   return sdd_launch(recv_rows, w1, row_slot, row_block_expert, row_offsets, h_blocks,
                     static_cast<int64_t>(num_ranks) * capacity, d_model, ffn_dim, experts_local, num_row_blocks, 1, 1, nullptr,

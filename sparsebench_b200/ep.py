@@ -126,13 +126,21 @@ class CudaOps:
         topo = DeviceTopology(BLOCK_SIZE, recv_counts.shape[1], ffn_dim // BLOCK_SIZE, *out[:8])
         return (topo, out[8]) if arrival_order else topo
 
-    def sdd_dispatch(self, peer, w1, topo, order, x, sorted_token, expert_offsets, my_rank, capacity):
-        """SDD over rows that are still arriving, with this rank's own pushes in the same kernel."""
+    def sdd_dispatch(self, peer, w1, topo, order, x, sorted_token, expert_offsets, my_rank, capacity, push_warps=-1):
+        """SDD over rows that are still arriving; this rank's own pushes run in the same kernel (push_warps != 0) or
+        in a push_rows_flagged launched before it on another stream (push_warps = 0)."""
         from sparsebench_b200 import _C
 
         return _C.ep_sdd_dispatch(peer.recv, w1, topo.row_token, topo.row_block_expert, topo.row_offsets,
                                   topo.col_indices.numel(), x, sorted_token, expert_offsets, order, peer.peer_recv,
-                                  peer.peer_flags, peer.flags, peer.done, peer.epoch, my_rank, capacity)
+                                  peer.peer_flags, peer.flags, peer.done, peer.epoch, my_rank, capacity, push_warps)
+
+    def push_rows_flagged(self, peer, x, sorted_token, expert_offsets, my_rank, experts_per_rank, capacity) -> None:
+        """This rank's rows into their owners' receive buffers, one arrival flag per 256-row segment."""
+        from sparsebench_b200 import _C
+
+        _C.ep_push_rows_flagged(x, sorted_token, expert_offsets, peer.peer_recv, peer.peer_flags, peer.done, peer.epoch,
+                                my_rank, experts_per_rank, capacity)
 
 
 class PeerExchange:
@@ -205,7 +213,7 @@ class ExpertParallelMoE:
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
                  group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
                  exchange: str = "nccl", fuse_return: bool = True, micro_batches: int = 1,
-                 fuse_dispatch: bool = False) -> None:
+                 fuse_dispatch: bool = False, push_beside: bool = True) -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
         (source, destination) pair; None means T*k of the first call's batch (never overflows).
         `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
@@ -216,7 +224,9 @@ class ExpertParallelMoE:
         `fuse_dispatch` (peer exchange only): only the counts are exchanged before the owner's layout is
         built; the rows are pushed by extra warps of the owner's SDD kernel and every SDD tile waits for
         the segments its rows lie in, instead of pushing all rows and waiting for all ranks before SDD
-        starts. Off by default: as measured on 2, 4 and 8 B200s the separate push kernel is the faster form.
+        starts. `push_beside` (with fuse_dispatch): the rows are pushed by the stand-alone push kernel on a second
+        stream, launched before the SDD kernel and running beside it (the whole GPU's warps push, the SDD tiles
+        follow the arrivals), instead of by the SDD kernel's own six push warps per block.
         `micro_batches` (peer exchange only): the T local tokens are cut into that many equal parts, each
         a complete step with its own exchange buffers on its own stream, ordered so that part m+1 is
         dispatched while part m is computed and part m returns while part m+1 is computed. Same result
@@ -224,6 +234,8 @@ class ExpertParallelMoE:
         owner's matmuls are tensor-bound (many tokens per expert) and the exchange is a large share."""
         self.fuse_return = fuse_return
         self.fuse_dispatch = fuse_dispatch
+        self.push_beside = push_beside
+        self._push_streams: dict = {}
         self.micro_batches = int(micro_batches)
         if self.micro_batches < 1:
             raise ValueError("micro_batches must be >= 1")
@@ -406,9 +418,23 @@ class ExpertParallelMoE:
         ops.push_counts(counts, peer.peer_counts, self.rank, self.experts_local)
         ops.barrier(peer.peer_pads, peer.pad, peer.epoch, self.rank, self.status)  # counts only: nothing heavy to wait for
         mark("dispatch all-to-all")
+        beside = self.push_beside and hasattr(ops, "push_rows_flagged")
+        if beside:
+            # The push kernel goes first, on a stream of its own: it waits for nothing, so it makes progress
+            # whatever else is resident, and the SDD kernel launched after it finds rows arriving.
+            main = torch.cuda.current_stream()
+            side = self._push_streams.get(main)
+            if side is None:
+                side = self._push_streams[main] = torch.cuda.Stream(device=x.device)
+            side.wait_stream(main)  # after the counts barrier: the epoch word carries this step's value
+            with torch.cuda.stream(side):
+                ops.push_rows_flagged(peer, x, sorted_token, offsets, self.rank, self.experts_local, capacity)
         topo, order = ops.owner_layout(peer.counts, capacity, self.ffn_dim, arrival_order=True)
         mark("routing")
-        h = ops.sdd_dispatch(peer, self.w1, topo, order, x, sorted_token, offsets, self.rank, capacity)
+        h = ops.sdd_dispatch(peer, self.w1, topo, order, x, sorted_token, offsets, self.rank, capacity,
+                             0 if beside else -1)
+        if beside:
+            torch.cuda.current_stream().wait_stream(side)
         if after_dispatch is not None:
             after_dispatch()
         mark("SDD + GELU (fused)")

@@ -307,16 +307,22 @@ def test_flagged_push_leaves_what_the_plain_push_leaves_and_raises_the_segment_f
     assert bool((want_flags == 7).any()) and (capacity < 256 or bool((want_flags == 0).any()))
 
 
-@pytest.mark.parametrize("case", ["zipf", "random", "empty_middle"])
-def test_overlapped_dispatch_single_rank_is_the_plain_layer(case: str) -> None:
+PUSH_ENGINES = pytest.mark.parametrize("engine", ["0", "1"], ids=["push_warps", "bulk_copies"])
+
+
+@PUSH_ENGINES
+@pytest.mark.parametrize(("case", "d_model"), [("zipf", 256), ("random", 256), ("empty_middle", 256), ("zipf", 2048),
+                                               ("random", 4096)])
+def test_overlapped_dispatch_single_rank_is_the_plain_layer(case: str, d_model: int, engine: str, monkeypatch) -> None:
     # World size 1 with the exchange buffers in local memory: the SDD kernel pushes this rank's rows to
     # itself and waits for its own flags. Same rows, same kernels: bit-identical to moe_forward, in both
     # dispatch modes, eagerly and twice in a row (the second step must wait for the second epoch).
     from sparsebench_b200 import moe_forward
     from sparsebench_b200.ep import ExpertParallelMoE, _no_mark
 
+    monkeypatch.setenv("SB_PUSH_ENGINE", engine)  # read at every launch: rows pushed by warps or by bulk copies
     g = torch.Generator().manual_seed(2)
-    num_tokens, num_experts, d_model, ffn_dim = 300, 16, 256, 512
+    num_tokens, num_experts, ffn_dim = 300, 16, 512  # rows of 512 B, 4 KB and 8 KB: 4, 4 and 2 rows per bulk chunk
     w1 = (torch.randn(num_experts, d_model, ffn_dim, generator=g) / d_model**0.5).bfloat16().cuda()
     w2 = (torch.randn(num_experts, ffn_dim, d_model, generator=g) / ffn_dim**0.5).bfloat16().cuda()
     layer = ExpertParallelMoE(w1, w2, num_experts)
@@ -327,20 +333,23 @@ def test_overlapped_dispatch_single_rank_is_the_plain_layer(case: str) -> None:
         gate = torch.rand(num_tokens, 2, generator=g).bfloat16().cuda()
         idx = routing_case(case, num_tokens, num_experts, seed=step).cuda()
         want = moe_forward(x, idx, gate, w1, w2)
-        for overlapped in (True, False):
-            layer.fuse_dispatch = overlapped
+        # Overlapped with the push kernel beside the SDD kernel, overlapped with the SDD kernel's own pushes, separate.
+        for overlapped, beside in ((True, True), (True, False), (False, False)):
+            layer.fuse_dispatch, layer.push_beside = overlapped, beside
             out = layer._forward_part(x, idx, gate, _no_mark, peer, capacity, None)
             layer.check()
-            assert torch.equal(out, want), f"step {step}, overlapped={overlapped}"
+            assert torch.equal(out, want), f"step {step}, overlapped={overlapped}, beside={beside}"
 
 
-def test_two_virtual_ranks_overlapped_dispatch_matches_oracle() -> None:
+@PUSH_ENGINES
+def test_two_virtual_ranks_overlapped_dispatch_matches_oracle(engine: str, monkeypatch) -> None:
     # Two ranks' worth of data on one GPU, one rank's kernels at a time: rank 1's rows are pushed by the
     # stand-alone push kernel first (it waits for nothing), then rank 0's SDD pushes its own rows and finds
     # rank 1's flags already raised. Checks rank 0's SDD blocks against the oracle of the concatenated batch.
     from sparsebench_b200 import _C
     from sparsebench_b200.routing import DeviceTopology
 
+    monkeypatch.setenv("SB_PUSH_ENGINE", engine)
     ranks, num_tokens, num_experts, d_model, ffn_dim = 2, 200, 8, 256, 512
     experts_local, capacity = num_experts // ranks, 400
     g = torch.Generator().manual_seed(9)
@@ -382,7 +391,8 @@ def test_two_virtual_ranks_overlapped_dispatch_matches_oracle() -> None:
             torch.testing.assert_close(got[rb, :, r], want[rb, :, r], rtol=1.6e-2, atol=1.6e-2)
 
 
-def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers() -> None:
+@PUSH_ENGINES
+def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers(engine: str, monkeypatch) -> None:
     # Failure detection without a fault: two virtual ranks, rank 1 never pushes, so its arrival flags are
     # never raised. Rank 0's SDD waits its bounded second per tile role, records SB_DEV_TIMEOUT_DISPATCH in
     # the status word and winds down; the context stays usable.
@@ -391,6 +401,7 @@ def test_overlapped_dispatch_gives_up_with_a_status_when_a_source_never_delivers
     from sparsebench_b200 import _C
     from sparsebench_b200.routing import DeviceTopology
 
+    monkeypatch.setenv("SB_PUSH_ENGINE", engine)
     ranks, num_tokens, num_experts, d_model, ffn_dim, capacity = 2, 64, 4, 256, 256, 128
     experts_local = num_experts // ranks
     g = torch.Generator().manual_seed(1)
