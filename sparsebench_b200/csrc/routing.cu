@@ -119,67 +119,99 @@ struct LogitSource {
   static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
   static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-  // A 32-copy step holds 32 / k whole tokens. Lane j < 32 / k owns token j of the step: it walks the token's E
-  // logits once and keeps the k best in registers (insertion into a short sorted list), so the tokens of a step
-  // are done side by side instead of one after the other; a shuffle then hands every copy's lane its expert id.
+  // A 32-copy step holds 32 / k whole tokens, k consecutive lanes per token (one per copy). The k lanes of a token
+  // share its E logits (lane p scans experts p, p + k, ...: adjacent addresses), each keeps the k best of its share
+  // in registers (insertion into a short sorted list), and a butterfly of shuffles merges the k lists, after which
+  // every lane of the token holds the token's k best and takes the one of its copy. k is a template argument of
+  // the worker below: the lists are unrolled k deep, not 8 deep with predicates (every warp of the few routing
+  // blocks issues these instructions, so their count is the kernel's time).
   template <int kIters>
   __device__ __forceinline__ bool load(int64_t begin, int64_t end, int lane, int32_t (&ids)[kIters]) const {
-    const int tokens_per_step = 32 / k;
+    switch (k) {
+      case 1: return load_k<kIters, 1>(begin, end, lane, ids);
+      case 2: return load_k<kIters, 2>(begin, end, lane, ids);
+      case 4: return load_k<kIters, 4>(begin, end, lane, ids);
+      default: return load_k<kIters, 8>(begin, end, lane, ids);
+    }
+  }
+
+  // (v, id) goes in front of the first entry it beats: a larger logit (NaN above everything), or an equal one with
+  // a lower expert id (torch.topk's order); everything from there on moves down, what falls off the end is dropped.
+  template <int K>
+  static __device__ __forceinline__ void insert(float (&best)[K], int32_t (&best_id)[K], float v, int32_t id) {
+    bool shifting = false;
+#pragma unroll
+    for (int r = 0; r < K; ++r) {
+      const bool beats = best_id[r] < 0 || logit_ranks_before(v, best[r]) ||
+                         (!logit_ranks_before(best[r], v) && id < best_id[r]);
+      if (id >= 0 && (shifting || beats)) {
+        shifting = true;
+        const float tv = best[r];
+        const int32_t ti = best_id[r];
+        best[r] = v;
+        best_id[r] = id;
+        v = tv;
+        id = ti;
+      }
+    }
+  }
+
+  template <int kIters, int K>
+  __device__ __forceinline__ bool load_k(int64_t begin, int64_t end, int lane, int32_t (&ids)[kIters]) const {
+    const int pick = lane % K;
 #pragma unroll
     for (int it = 0; it < kIters; ++it) {
       ids[it] = -1;
       const int64_t step_begin = begin + it * 32;
       if (step_begin >= end) continue;  // uniform across the warp
-      const int64_t first_copy = step_begin + static_cast<int64_t>(lane) * k;
-      const bool owner = lane < tokens_per_step && first_copy < end;
-      float best[kRouterMaxK];
-      int32_t best_id[kRouterMaxK];
+      const int64_t copy = step_begin + lane;
+      const bool live = copy < end;  // the n copies are whole tokens, so a token's k lanes are live together
+      float best[K];
+      int32_t best_id[K];
 #pragma unroll
-      for (int r = 0; r < kRouterMaxK; ++r) {
+      for (int r = 0; r < K; ++r) {
         best[r] = -INFINITY;
         best_id[r] = -1;
       }
-      if (owner) {
-        const logit_t* row = logits + (first_copy / k) * num_experts;
-        for (int32_t e = 0; e < num_experts; ++e) {
-          float v = to_float(__ldg(row + e));
-          int32_t id = e;
-          // Insert (v, id) into the list of the k best so far: it goes in front of the first entry it strictly
-          // beats (equal values stay behind the earlier, lower id), everything from there on moves down one
-          // place, and what falls off the end is dropped.
-          bool shifting = false;
+      if (live) {
+        const logit_t* row = logits + (copy / K) * num_experts;
+        // Eight loads in flight before the first is used: one at a time, the walk is a chain of memory latencies
+        // (a 32-byte sector lasts the token's lanes four steps at k = 2) on the few SMs this kernel runs on.
+        for (int32_t e0 = pick; e0 < num_experts; e0 += 8 * K) {
+          float v[8];
 #pragma unroll
-          for (int r = 0; r < kRouterMaxK; ++r) {
-            if (r < k && (shifting || best_id[r] < 0 || logit_ranks_before(v, best[r]))) {
-              shifting = true;
-              const float tv = best[r];
-              const int32_t ti = best_id[r];
-              best[r] = v;
-              best_id[r] = id;
-              v = tv;
-              id = ti;
-            }
-          }
-        }
-        float denom = 0.0f;
+          for (int u = 0; u < 8; ++u) v[u] = e0 + u * K < num_experts ? to_float(__ldg(row + e0 + u * K)) : 0.0f;
 #pragma unroll
-        for (int r = 0; r < kRouterMaxK; ++r)
-          if (r < k) denom += __expf(best[r] - best[0]);
-#pragma unroll
-        for (int r = 0; r < kRouterMaxK; ++r) {
-          if (r < k) {
-            expert_idx[first_copy + r] = best_id[r];
-            store(expert_weight + first_copy + r, __expf(best[r] - best[0]) / denom);
-          }
+          for (int u = 0; u < 8; ++u) insert<K>(best, best_id, v[u], e0 + u * K < num_experts ? e0 + u * K : -1);
         }
       }
-      // Copy `lane` of the step belongs to token lane / k, pick lane % k: fetch it from the owner's registers.
-      const int src = lane / k;
-      const int pick = lane - src * k;
 #pragma unroll
-      for (int r = 0; r < kRouterMaxK; ++r) {
-        const int32_t from_owner = __shfl_sync(kFullMask, best_id[r], src);
-        if (r == pick && step_begin + lane < end) ids[it] = from_owner;
+      for (int d = 1; d < K; d <<= 1) {  // the partner's list is merged entry by entry (an id of -1 is no entry)
+        float theirs[K];
+        int32_t their_id[K];
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+          theirs[r] = __shfl_xor_sync(kFullMask, best[r], d);
+          their_id[r] = __shfl_xor_sync(kFullMask, best_id[r], d);
+        }
+#pragma unroll
+        for (int r = 0; r < K; ++r) insert<K>(best, best_id, theirs[r], their_id[r]);
+      }
+      if (live) {
+        float denom = 0.0f;
+#pragma unroll
+        for (int r = 0; r < K; ++r) denom += __expf(best[r] - best[0]);
+        float mine = best[0];
+        int32_t mine_id = best_id[0];
+#pragma unroll
+        for (int r = 1; r < K; ++r)
+          if (r == pick) {
+            mine = best[r];
+            mine_id = best_id[r];
+          }
+        expert_idx[copy] = mine_id;
+        store(expert_weight + copy, __expf(mine - best[0]) / denom);
+        ids[it] = mine_id;
       }
     }
     return false;
