@@ -562,7 +562,12 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     sums: dict[str, float] = {}
     iters = max(5, min(args.steps, 30))
     for it in range(iters + 2):
+        if world > 1:
+            dist.barrier()  # the ranks start the step together, as they do inside the timed graph replays
         flush_l2(flush)
+        # About a millisecond of GPU time in front of the step: the eager launches below queue up behind it, so that
+        # an event pair brackets device work and not the host's launch latency (a busy host inflated the stages).
+        torch.cuda._sleep(2_000_000)
         events = [torch.cuda.Event(enable_timing=True)]
         events[0].record()
         seen: list[str] = []
