@@ -30,3 +30,24 @@ def test_non_zero_ranks_of_the_reference_arm_do_no_work() -> None:
     proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
                           capture_output=True, text=True, timeout=120, env={**__import__("os").environ, **env})
     assert proc.returncode == 0 and proc.stdout.strip() == ""
+
+
+def test_expert_parallel_form_follows_the_flags_and_the_measured_table() -> None:
+    # Which form of the peer-exchange step the benchmark runs: --ep-dispatch wins, the older flag means "separate",
+    # otherwise the per-rank-count table; every listed rank count has a micro-batch default of at least one.
+    import types
+
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench_ep
+
+    def wanted(world: int, **flags) -> bool:
+        return bench_ep.overlapped_dispatch_wanted(types.SimpleNamespace(**flags), world)
+
+    for world, (overlapped, micro_batches) in bench_ep.DEFAULT_EP_FORM.items():
+        assert wanted(world) is overlapped and wanted(world, ep_dispatch="auto") is overlapped
+        assert micro_batches >= 1 and bench_ep.DEFAULT_MICRO_BATCHES[world] == micro_batches
+    assert wanted(3) is False, "rank counts without a measurement run the plainest form"
+    for world in (2, 4, 8):
+        assert wanted(world, ep_dispatch="overlapped") and wanted(world, ep_dispatch="beside")
+        assert not wanted(world, ep_dispatch="separate")
+        assert not wanted(world, ep_dispatch="overlapped", ep_unfused_dispatch=True)
