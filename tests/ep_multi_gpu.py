@@ -164,7 +164,7 @@ def main() -> None:
     exchange = "peer" if mode.startswith("peer") else mode
     layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
                               capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused",
-                              fuse_dispatch=mode != "peer_nodispatch",
+                              fuse_dispatch=mode != "peer_nodispatch", push_beside=mode != "peer_warps",
                               micro_batches=int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1)
     mine = slice(rank * T, (rank + 1) * T)
 

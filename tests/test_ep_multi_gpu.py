@@ -51,7 +51,9 @@ def test_benchmark_shape_matches_oracle_on_every_rank(world: int, form: str) -> 
         assert f"rank {rank}/{world}: expert-parallel parity ok" in text, text[-3000:]
 
 
-@pytest.mark.parametrize("mode", ["nccl", "peer_unfused", "peer_nodispatch", "peer_mb2"])
+# "peer": dispatch overlapped, the push kernel on a second stream beside SDD; "peer_warps": pushed by SDD's own warps;
+# "peer_nodispatch": separate push kernel and barrier; "peer_unfused": two-kernel return; "peer_mb2": two micro-batches.
+@pytest.mark.parametrize("mode", ["nccl", "peer", "peer_warps", "peer_unfused", "peer_nodispatch", "peer_mb2"])
 def test_other_exchange_modes_small_shape(mode: str) -> None:
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
