@@ -643,6 +643,8 @@ def main() -> None:
     parser.add_argument("--ep-micro-batches", type=int, default=0,
                         help="N > 1, peer exchange: cut each step into this many pipelined micro-batches "
                              "(0 = the default for this N)")
+    parser.add_argument("--ep-micro-split", default="",
+                        help="N > 1, peer exchange: shares of the micro-batches, e.g. 0.25,0.75 (default: equal shares)")
     parser.add_argument("--profile", action="store_true", help="run 3 eager layer calls and exit (for ncu)")
     parser.add_argument("--profile-front-ends", action="store_true",
                         help="with --profile: run the router, token-rounding and assignment-list front ends of the layer")

@@ -34,6 +34,8 @@ PARITY_ROWS_PER_RANK = 32
 # owner's SDD kernel, micro-batches pipelined over streams). Rank counts that are not listed run the plainest form.
 DEFAULT_EP_FORM: dict[int, tuple[bool, int]] = {2: (False, 1), 4: (False, 1), 8: (False, 2)}
 DEFAULT_MICRO_BATCHES: dict[int, int] = {n: form[1] for n, form in DEFAULT_EP_FORM.items()}
+# Unequal shares of the micro-batches where measured to pay (the first part's dispatch is the one nothing hides).
+DEFAULT_MICRO_FRACTIONS: dict[int, tuple[float, ...]] = {}
 
 
 def overlapped_dispatch_wanted(args, world: int) -> bool:
@@ -425,6 +427,13 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
     exchange = getattr(args, "ep_exchange", "peer") if world > 1 else "nccl"
     # Micro-batches pipelined over streams (peer exchange): 0 = this build's default for the rank count.
     micro_batches = getattr(args, "ep_micro_batches", 0) or DEFAULT_MICRO_BATCHES.get(world, 1)
+    # Shares of the micro-batches ("0.25,0.75"); empty = the default for this rank count, else equal shares.
+    split = getattr(args, "ep_micro_split", "") or ""
+    micro_fractions = tuple(float(f) for f in split.split(",")) if split else None
+    if micro_fractions is None and not getattr(args, "ep_micro_batches", 0):
+        micro_fractions = DEFAULT_MICRO_FRACTIONS.get(world)
+    if micro_fractions is not None:
+        micro_batches = len(micro_fractions)
     moe = None
     if exchange == "peer":
         # Rows stored straight into the owner's memory: only real rows travel, so the capacity can be
@@ -434,6 +443,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                                     fuse_return=not getattr(args, "ep_unfused_return", False),
                                     fuse_dispatch=overlapped_dispatch_wanted(args, world),
                                     push_beside=getattr(args, "ep_dispatch", "auto") != "overlapped",
+                                    micro_fractions=micro_fractions,
                                     micro_batches=micro_batches)
             mapped = torch.ones(1, device=device)
         except Exception as exc:  # noqa: BLE001 - reported in the JSON line
@@ -475,7 +485,8 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
         torch.cuda.synchronize()
         _C.device_status(device).zero_()
         moe = ExpertParallelMoE(dev.w1, dev.w2, cfg.num_experts, capacity=n_copies, exchange="peer",
-                                fuse_return=moe.fuse_return, fuse_dispatch=False, micro_batches=moe.micro_batches)
+                                fuse_return=moe.fuse_return, fuse_dispatch=False, micro_batches=moe.micro_batches,
+                                micro_fractions=moe.micro_fractions)
         out, parity = first_step_ok(moe)
 
     # ---- value: graph replay if the collectives capture, else eager --------------------------------
@@ -656,6 +667,7 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                    "exchange": exchange, "return_leg": "stored by the DSD epilogue" if fused_return else "separate kernel",
                    "dispatch_leg": dispatch_leg, "dispatch_fallback": fallback_note,
                    "micro_batches": timed_moe.micro_batches,
+                   "micro_fractions": [round(f, 4) for f in timed_moe.micro_fractions],
                    "launch": launch, "l2": "256 MiB written and read back before every step (L2 cold and clean)",
                    "frac_of_bf16_peak": value / world / bf16_tflops},
         "parity": parity,

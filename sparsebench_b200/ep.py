@@ -37,6 +37,8 @@ be exercised on CPU ranks with a stand-in from the tests; the default is the CUD
 
 from __future__ import annotations
 
+import math
+
 from collections.abc import Callable
 from dataclasses import dataclass
 
@@ -213,7 +215,8 @@ class ExpertParallelMoE:
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, num_experts: int,
                  group: dist.ProcessGroup | None = None, capacity: int | None = None, ops: object | None = None,
                  exchange: str = "nccl", fuse_return: bool = True, micro_batches: int = 1,
-                 fuse_dispatch: bool = False, push_beside: bool = True) -> None:
+                 fuse_dispatch: bool = False, push_beside: bool = True,
+                 micro_fractions: tuple[float, ...] | None = None) -> None:
         """w1_local [E/N, D, F], w2_local [E/N, F, D]: this rank's experts. `capacity` = rows per
         (source, destination) pair; None means T*k of the first call's batch (never overflows).
         `exchange`: "nccl" = fixed-capacity all-to-all collectives (every slot travels, real or not);
@@ -231,7 +234,10 @@ class ExpertParallelMoE:
         a complete step with its own exchange buffers on its own stream, ordered so that part m+1 is
         dispatched while part m is computed and part m returns while part m+1 is computed. Same result
         bit for bit; every part reads the owner's expert weights again, so it pays only where the
-        owner's matmuls are tensor-bound (many tokens per expert) and the exchange is a large share."""
+        owner's matmuls are tensor-bound (many tokens per expert) and the exchange is a large share.
+        `micro_fractions`: the parts' shares of the tokens instead of equal ones (one per micro-batch, summing
+        to 1, the same on every rank): the first part's dispatch is the only one nothing hides, so a smaller
+        first part shortens the step."""
         self.fuse_return = fuse_return
         self.fuse_dispatch = fuse_dispatch
         self.push_beside = push_beside
@@ -239,6 +245,12 @@ class ExpertParallelMoE:
         self.micro_batches = int(micro_batches)
         if self.micro_batches < 1:
             raise ValueError("micro_batches must be >= 1")
+        if micro_fractions is None:
+            micro_fractions = tuple(1.0 / self.micro_batches for _ in range(self.micro_batches))
+        if len(micro_fractions) != self.micro_batches or abs(sum(micro_fractions) - 1.0) > 1e-6 or \
+                min(micro_fractions) <= 0.0:
+            raise ValueError("micro_fractions needs one positive share per micro-batch, summing to 1")
+        self.micro_fractions = tuple(float(f) for f in micro_fractions)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -265,11 +277,12 @@ class ExpertParallelMoE:
             if self.micro_batches == 1:
                 self.peer = PeerExchange(pg, w1_local.device, capacity, d_model, experts_local, w1_local.dtype)
             else:
-                if capacity % self.micro_batches:
-                    raise ValueError(f"capacity {capacity} does not split into {self.micro_batches} micro-batches")
-                self.part_capacity = capacity // self.micro_batches
-                for _ in range(self.micro_batches):
-                    self.part_peers.append(PeerExchange(pg, w1_local.device, self.part_capacity, d_model, experts_local,
+                # Every part gets its share of the capacity, rounded up to whole blocks of 128 rows plus one block
+                # (the part boundaries are rounded to 8 tokens, so a part may hold a few rows more than its share).
+                self.part_capacities = [min(capacity, -(-int(math.ceil(capacity * f)) // 128) * 128 + 128)
+                                        for f in self.micro_fractions]
+                for part_capacity in self.part_capacities:
+                    self.part_peers.append(PeerExchange(pg, w1_local.device, part_capacity, d_model, experts_local,
                                                         w1_local.dtype))
                     self.part_streams.append(torch.cuda.Stream(device=w1_local.device))
                 self.peer = self.part_peers[0]
@@ -308,23 +321,27 @@ class ExpertParallelMoE:
         joined back into the caller's stream, so it captures into one graph). Part m+1 may not start
         its dispatch before part m's rows have arrived (the two would only share the links), but
         does not wait for part m's matmuls: that is where the overlap comes from."""
-        parts = self.micro_batches
         num_tokens = x.shape[0]
-        if num_tokens % parts:
-            raise ValueError(f"{num_tokens} tokens do not split into {parts} micro-batches")
-        step = num_tokens // parts
+        # Part boundaries from the shares, on multiples of 8 tokens (the last part takes the remainder).
+        bounds, running = [0], 0.0
+        for f in self.micro_fractions[:-1]:
+            running += f
+            bounds.append(min(num_tokens, max(bounds[-1], int(round(running * num_tokens / 8.0)) * 8)))
+        bounds.append(num_tokens)
         main = torch.cuda.current_stream()
         outs: list[torch.Tensor] = []
         dispatched: torch.cuda.Event | None = None
         for m, (peer, stream) in enumerate(zip(self.part_peers, self.part_streams)):
-            rows = slice(m * step, (m + 1) * step)
+            rows = slice(bounds[m], bounds[m + 1])
+            if rows.stop == rows.start:
+                raise ValueError(f"{num_tokens} tokens leave micro-batch {m} empty with shares {self.micro_fractions}")
             stream.wait_stream(main)
             with torch.cuda.stream(stream):
                 if dispatched is not None:
                     stream.wait_event(dispatched)
                 arrived = torch.cuda.Event()
                 out = self._forward_part(x[rows], expert_idx[rows], expert_weight[rows], mark if m == 0 else _no_mark,
-                                         peer, self.part_capacity, arrived.record)
+                                         peer, self.part_capacities[m], arrived.record)
                 out.record_stream(main)
             outs.append(out)
             dispatched = arrived

@@ -165,7 +165,9 @@ def main() -> None:
     layer = ExpertParallelMoE(shard_experts(w1, rank, world).cuda(), shard_experts(w2, rank, world).cuda(), E,
                               capacity=T * K, exchange=exchange, fuse_return=mode != "peer_unfused",
                               fuse_dispatch=mode != "peer_nodispatch", push_beside=mode != "peer_warps",
-                              micro_batches=int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1)
+                              micro_batches=2 if mode == "peer_split" else
+                              int(mode[len("peer_mb"):]) if mode.startswith("peer_mb") else 1,
+                              micro_fractions=(0.25, 0.75) if mode == "peer_split" else None)
     mine = slice(rank * T, (rank + 1) * T)
 
     def check(out: torch.Tensor, x, idx, gate, what: str) -> None:

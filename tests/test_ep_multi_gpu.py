@@ -52,8 +52,9 @@ def test_benchmark_shape_matches_oracle_on_every_rank(world: int, form: str) -> 
 
 
 # "peer": dispatch overlapped, the push kernel on a second stream beside SDD; "peer_warps": pushed by SDD's own warps;
-# "peer_nodispatch": separate push kernel and barrier; "peer_unfused": two-kernel return; "peer_mb2": two micro-batches.
-@pytest.mark.parametrize("mode", ["nccl", "peer", "peer_warps", "peer_unfused", "peer_nodispatch", "peer_mb2"])
+# "peer_nodispatch": separate push kernel and barrier; "peer_unfused": two-kernel return; "peer_mb2": two micro-batches;
+# "peer_split": two micro-batches of a quarter and three quarters of the tokens.
+@pytest.mark.parametrize("mode", ["nccl", "peer", "peer_warps", "peer_unfused", "peer_nodispatch", "peer_mb2", "peer_split"])
 def test_other_exchange_modes_small_shape(mode: str) -> None:
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
