@@ -231,6 +231,33 @@ def host_link_gbs(device: torch.device, world: int) -> dict:
             dist.all_reduce(total, op=dist.ReduceOp.SUM)
             dist.all_reduce(least, op=dist.ReduceOp.MIN)
         out[name] = {"all_ranks_gbs": float(total.item()), "slowest_rank_gbs": float(least.item())}
+    # Both directions at once on two streams, as the pipelined end-to-end loop runs them: bytes moved either way per
+    # second. The loop cannot be faster than (bytes in + bytes out per step) / this figure.
+    dev_out = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    host_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    inbound, outbound = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    inbound.wait_event(start)
+    outbound.wait_event(start)
+    for _ in range(4):
+        with torch.cuda.stream(inbound):
+            dev.copy_(host, non_blocking=True)
+        with torch.cuda.stream(outbound):
+            host_out.copy_(dev_out, non_blocking=True)
+    torch.cuda.current_stream().wait_stream(inbound)
+    torch.cuda.current_stream().wait_stream(outbound)
+    end.record()
+    end.synchronize()
+    mine = torch.tensor([8 * nbytes / (start.elapsed_time(end) * 1e-3) / 1e9], dtype=torch.float64, device=device)
+    total, least = mine.clone(), mine.clone()
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+        dist.all_reduce(least, op=dist.ReduceOp.MIN)
+    out["both_directions"] = {"all_ranks_gbs": float(total.item()), "slowest_rank_gbs": float(least.item())}
     return out
 
 
@@ -677,7 +704,9 @@ def measure(args, metric: str, peaks: tuple[float, float, str], clock_sampler_cl
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "how": "steps pipelined over three streams (copy in, step, copy out), two sets of staging buffers; "
                        "every step's H2D and D2H copies are inside the timed region",
-                "single_step_latency_ms": e2e_latency_ms, "host_link_all_ranks_copying": host_link},
+                "single_step_latency_ms": e2e_latency_ms, "host_link_all_ranks_copying": host_link,
+                # What the host link allows: this rank's bytes per step over its share of the bidirectional rate.
+                "host_link_floor_ms": (h2d + d2h) / (host_link["both_directions"]["slowest_rank_gbs"] * 1e9) * 1e3},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": roofline,
     }
